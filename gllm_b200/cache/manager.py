@@ -84,8 +84,8 @@ class CacheManager:
         self._entry_group: list[int | None] = []
         self._entry_layer: list[int | None] = []
         self._entry_writes: list[bool] = []
-        self._states: list[torch.Tensor | None] = []
-        self._state_reqs: list[StateRequirement | None] = []
+        self._states: list[tuple[torch.Tensor, ...] | None] = []
+        self._state_reqs: list[tuple[StateRequirement, ...] | None] = []
         by_req: dict[KVPageRequirement, CacheGroup] = {}
         for idx, (kv, state, reads) in enumerate(requirements):
             if reads is not None:
@@ -110,12 +110,15 @@ class CacheManager:
                 self._entry_group.append(None)
                 self._entry_layer.append(None)
             self._entry_writes.append(True)
-            self._state_reqs.append(state)
-            if state is not None and allocate_pools:
+            # a mixer may ask for one state tensor or for several
+            wanted = () if state is None else (tuple(state) if isinstance(state, (tuple, list)) else (state,))
+            self._state_reqs.append(wanted or None)
+            if wanted and allocate_pools:
                 # one row more than there are slots: the null row, for rows that pad a batch
-                self._states.append(
-                    torch.zeros((self.max_batch_size + 1, *state.shape), dtype=state.dtype, device=self.device)
-                )
+                self._states.append(tuple(
+                    torch.zeros((self.max_batch_size + 1, *s.shape), dtype=s.dtype, device=self.device)
+                    for s in wanted
+                ))
             else:
                 self._states.append(None)
         for g in self.groups:
@@ -162,9 +165,10 @@ class CacheManager:
         slot = self.slots.allocate()
         rc = RequestCache(request_id, slot, 0, {g.index: [] for g in self.groups})
         self.requests[request_id] = rc
-        for state in self._states:
-            if state is not None:
-                state[slot].zero_()
+        for idx, states in enumerate(self._states):
+            if states is not None and self._entry_writes[idx]:
+                for state in states:
+                    state[slot].zero_()
         return rc
 
     def pages_needed(self, request_id, n_new: int) -> dict[int, int]:
@@ -307,7 +311,9 @@ class CacheManager:
             pages = None
             if g is not None and self.groups[g].pool is not None:
                 pages = self.groups[g].pool[self._entry_layer[idx]]
-            out.append(MixerCache(group=g, pages=pages, writes=self._entry_writes[idx], state=self._states[idx],
+            states = self._states[idx] or ()
+            out.append(MixerCache(group=g, pages=pages, writes=self._entry_writes[idx],
+                                  state=states[0] if states else None, states=tuple(states),
                                   requirement=None if g is None else self.groups[g].requirement,
                                   block_size=self.block_size))
         return out

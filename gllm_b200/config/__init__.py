@@ -2,6 +2,7 @@
 caller chooses for generation (GeneratorParams)."""
 
 from gllm_b200.config.generator_params import GeneratorParams
+from gllm_b200.config.guvetar_config import GuvetarConfig
 from gllm_b200.config.llama_config import LlamaConfig, RopeScaling
 from gllm_b200.config.model_config import ConfigError, ModelConfig, load_config
 from gllm_b200.config.registry import (
@@ -14,6 +15,7 @@ from gllm_b200.config.registry import (
 __all__ = [
     "GeneratorParams",
     "ConfigError",
+    "GuvetarConfig",
     "LlamaConfig",
     "ModelConfig",
     "RopeScaling",

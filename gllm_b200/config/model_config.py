@@ -76,6 +76,8 @@ def load_config(source: str | os.PathLike | dict[str, Any]) -> ModelConfig:
         with open(path, "r") as f:
             d = json.load(f)
     archs = d.get("architectures")
+    if isinstance(d.get("architecture"), str):          # some designs name theirs with a plain string
+        archs = [d["architecture"]]
     if not archs or not isinstance(archs, list):
         raise ConfigError("config.json lacks 'architectures': cannot choose a model class")
     arch = architecture_for(archs[0])

@@ -34,7 +34,8 @@ def register_architecture(name: str, config_class, build_spec) -> Architecture:
 
 
 def _ensure_builtin_loaded() -> None:
-    # The built-in architecture registers itself on import.
+    # The built-in architectures register themselves on import.
+    import gllm_b200.models.guvetar  # noqa: F401
     import gllm_b200.models.llama  # noqa: F401
 
 

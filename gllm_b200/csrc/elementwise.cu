@@ -898,3 +898,43 @@ GLLM_API int gllm_rope_store_bf16(__nv_bfloat16* qkv, const float* parts, int n_
                                           cache, n_tokens, hq, hkv, d, rotary_dim, interleaved, block_size,
                                           num_pages, status, stream);
 }
+
+// ---------------------------------------------------------------- squared ReLU, weighted sum of two branches
+// out = max(x, 0)^2 (the activation of a dense feed-forward without a gate), and out = a * x + b * y
+// (two mixers that run side by side on the same input), both computed in fp32.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256)
+relu_sq_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  const float v = fmaxf(to_float(x[i]), 0.f);
+  out[i] = from_float<T>(v * v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+scaled_sum_kernel(const T* __restrict__ x, const T* __restrict__ y, T* __restrict__ out, float a, float b, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n) return;
+  out[i] = from_float<T>(fmaf(b, to_float(y[i]), a * to_float(x[i])));
+}
+}  // namespace
+
+#define GLLM_POINTWISE_EXPORTS(T, S)                                                                      \
+  GLLM_API int gllm_relu_sq_##S(const T* x, T* out, int64_t n, cudaStream_t stream) {                     \
+    if (n <= 0) return 0;                                                                                 \
+    return gllm_launch(relu_sq_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, out, n); \
+  }                                                                                                       \
+  GLLM_API int gllm_scaled_sum_##S(const T* x, const T* y, T* out, float a, float b, int64_t n,           \
+                                   cudaStream_t stream) {                                                 \
+    if (n <= 0) return 0;                                                                                 \
+    return gllm_launch(scaled_sum_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, y, out, a, \
+                       b, n);                                                                             \
+  }
+GLLM_POINTWISE_EXPORTS(float, f32)
+GLLM_POINTWISE_EXPORTS(__nv_bfloat16, bf16)

@@ -28,13 +28,13 @@ def _build_layer(layer_spec) -> Block:
     except KeyError:
         raise KeyError(f"no block of kind {layer_spec.block!r} is registered; known: {sorted(BLOCKS)}") from None
     declared = block_cls.part_kinds
-    missing = [n for n in declared if n not in layer_spec.parts]
+    missing = [n for n in declared if n not in layer_spec.parts and n not in block_cls.optional_parts]
     extra = [n for n in layer_spec.parts if n not in declared]
     if missing or extra:
         raise ValueError(f"block {layer_spec.block!r} declares parts {list(declared)}: the layer lacks {missing} "
                          f"and names {extra} beyond them")
     return block_cls(**{name: build_part(_TABLE_OF_KIND[kind], layer_spec.parts[name])
-                        for name, kind in declared.items()})
+                        for name, kind in declared.items() if name in layer_spec.parts})
 
 
 def expected_tensors_of_spec(spec: ModelSpec) -> dict[str, TensorExpectation]:
@@ -64,6 +64,7 @@ class DecoderModel:
         self.final_norm: Norm = build_part(NORMS, spec.final_norm)
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
+        self._frequencies: torch.Tensor | None = None
 
     @property
     def graph_safe_portions(self) -> bool:
@@ -93,6 +94,7 @@ class DecoderModel:
                 part.load(get, self.dtype, self.device)
         self.final_norm.load(get, self.dtype, self.device)
         self.head = self.embedding if self.spec.head_name is None else get(self.spec.head_name, "matrix")
+        self._sinusoid_frequencies()
 
     # ------------------------------------------------------------------ cache
     def cache_requirements(self):
@@ -116,6 +118,17 @@ class DecoderModel:
                 needs.setdefault(key, set()).update(values)
         return needs
 
+    def _sinusoid_frequencies(self):
+        """fp32 ``[ceil(width / 2)]``: ``base ** (-2i / width)``, formed in float64 and rounded once."""
+        base = self.spec.position_sinusoid_base
+        if base is None:
+            return None
+        if self._frequencies is None:
+            i = torch.arange((self.spec.hidden_size + 1) // 2, dtype=torch.float64)
+            freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / self.spec.hidden_size)
+            self._frequencies = freq.to(torch.float32).to(self.device)
+        return self._frequencies
+
     # ---------------------------------------------------------------- forward
     def forward(
         self,
@@ -126,8 +139,15 @@ class DecoderModel:
         logits_out: torch.Tensor | None = None,
     ) -> torch.Tensor:
         """Logits ``[len(logit_rows), vocab]`` fp32 of the flat batch ``tokens``."""
-        resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row,
-                              scale=1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
+        scale = 1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale
+        if self.spec.position_sinusoid_base is not None or self.spec.residual_streams > 1:
+            from gllm_b200.ops import stateful
+
+            resid = stateful.embed_streams(tokens, self.embedding, ctx.positions, self._sinusoid_frequencies(),
+                                           streams=self.spec.residual_streams, sampled=ctx.sampled,
+                                           token_row=ctx.token_row, scale=scale)
+        else:
+            resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row, scale=scale)
         branch = None
         for entry_idx, entry in enumerate(self.spec.plan):
             branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])

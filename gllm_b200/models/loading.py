@@ -28,6 +28,7 @@ def load_model(folder: str, dtype: str | None = None, device: str | torch.device
         # the kernels this model will ask for are compiled now, side by side, if they are not built yet
         from gllm_b200 import ops
 
-        ops.prepare(model.dtype, model.kernel_needs().get("attention_head_dims", ()))
+        needs = model.kernel_needs()
+        ops.prepare(model.dtype, needs.get("attention_head_dims", ()), modules=sorted(needs.get("modules", ())))
     model.load(open_checkpoint(folder))
     return config, model

@@ -79,6 +79,12 @@ class ModelSpec:
     embedding_scale: float | None = None
     logit_scale: float | None = None
     logit_softcap: float | None = None
+    # With a base b: column 2i of the looked-up embedding gets sin(p * b^(-2i/width)) added and column
+    # 2i+1 the cosine of the same angle, p being the token's position (positions enter nowhere else then).
+    position_sinusoid_base: float | None = None
+    # The residual is kept as this many parallel streams ``[tokens, streams * hidden]``, all equal to the
+    # embedding at the start; the layers' norms say how sublayers read and write them.
+    residual_streams: int = 1
     # Tensor names that a checkpoint may hold and the model does not read
     # (for instance a stored head beside tied embeddings).
     ignorable_names: tuple[str, ...] = ()

@@ -41,6 +41,8 @@ __all__ = [
     "interleave_gate_up",
     "add_bias",
     "rmsnorm_heads",
+    "relu_sq",
+    "scaled_sum",
 ]
 
 P = c_void_p
@@ -54,6 +56,8 @@ _SIGNATURES = {
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
+        "gllm_relu_sq_{t}": [P, P, c_int64, P],
+        "gllm_scaled_sum_{t}": [P, P, P, c_float, c_float, c_int64, P],
         "gllm_rope_store_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, P, P],
     },
@@ -63,6 +67,25 @@ _SIGNATURES = {
     "sampling": {
         "gllm_sample": [P, c_int64, c_int, c_int, P, P, P, P, P, P, c_int, P, P, P, P, P, P, P],
         "gllm_argmax": [P, c_int64, c_int, c_int, P, P, P],
+    },
+    "recurrent": {
+        "gllm_conv_silu_{t}": [P, c_int64, P, P, P, P, P, P, c_int, c_int, c_int, P],
+        "gllm_selective_scan_{t}": [P, P, P, P, P, c_int64, c_int, c_int, P, P, c_int64, c_int, P, P, P, P, P, c_int,
+                                    c_int, c_int, c_int, P],
+        "gllm_matrix_recurrence_{t}": [c_int, P, c_int64, P, c_int64, P, c_int64, P, c_int64, P, P, c_float, c_float,
+                                       P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, P],
+        "gllm_head_norm_{t}": [P, c_int64, c_int, c_int, c_float, P, c_int, P, c_int64, P, c_int64, c_int, c_int,
+                               c_int, c_float, P],
+    },
+    "hyper_streams": {
+        "gllm_embed_streams_{t}": [P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_float, P, P],
+        "gllm_stream_mix_norm_{t}": [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, P],
+    },
+    "attention_sigmoid": {
+        "gllm_qk_norm_store_{t}": [P, c_int64, P, P, c_float, c_float, c_float, P, P, P, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, P, P],
+        "gllm_attention_sigmoid_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_float, P, P],
     },
     "attention_simt": {
         "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
@@ -103,26 +126,33 @@ def _error_string(code: int) -> str:
         return f"cudaError {code}"
 
 
-def modules_for(dtype: torch.dtype, head_dims=(), sampling: bool = False) -> list[str]:
-    """The kernel modules a model of this compute dtype with mixers of these head sizes will load."""
+def modules_for(dtype: torch.dtype, head_dims=(), sampling: bool = False, modules=()) -> list[str]:
+    """The kernel modules a model of this compute dtype will load: the products and pointwise kernels
+    always, the softmax-attention modules when a mixer names a head size (``head_dims``), and whatever
+    else its parts name (``modules``: the kernels of mixers with a state, of the streamed residual ...)."""
     if dtype == torch.float32:
-        names = ["elementwise", "gemm_fp32", "attention_simt"]
+        names = ["elementwise", "gemm_fp32"]
+        if head_dims:
+            names.append("attention_simt")
     else:
-        names = ["elementwise", "gemm_bf16", "gemm_bf16_pair", "attention_bf16", "attention_prefill_bf16"]
+        names = ["elementwise", "gemm_bf16", "gemm_bf16_pair"]
+        if head_dims:
+            names += ["attention_bf16", "attention_prefill_bf16"]
         if any(d in (64, 128) for d in head_dims):
             names += ["attention_prefill_tmem", "attention_decode_tma"]
         if any(d not in (32, 64, 128) for d in head_dims):
             names.append("attention_simt")
+    names += [m for m in modules if m not in names]
     if sampling:
         names.append("sampling")
     return names
 
 
-def prepare(dtype: torch.dtype, head_dims=(), sampling: bool = False) -> None:
+def prepare(dtype: torch.dtype, head_dims=(), sampling: bool = False, modules=()) -> None:
     """Compile (side by side) whatever of ``modules_for`` is not built yet."""
     from gllm_b200.ops.build import compile_modules
 
-    compile_modules(modules_for(dtype, head_dims, sampling))
+    compile_modules(modules_for(dtype, head_dims, sampling, modules))
 
 
 # number of kernel launches made through this module (benchmarks read it)
@@ -438,6 +468,27 @@ def linear_gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return silu_mul(linear(x, weight), block=GATED_BLOCK)
 
 
+def relu_sq(x: torch.Tensor) -> torch.Tensor:
+    """``max(x, 0) ** 2``: the activation of a dense feed-forward without a gate."""
+    _cuda(x, "x")
+    out = torch.empty_like(x)
+    f = _fn("elementwise", f"gllm_relu_sq_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), out.data_ptr(), x.numel(), _stream()), "relu_sq")
+    return out
+
+
+def scaled_sum(x: torch.Tensor, y: torch.Tensor, a: float, b: float) -> torch.Tensor:
+    """``a * x + b * y`` (computed in fp32) of two tensors of equal shape and type."""
+    _cuda(x, "x")
+    _cuda(y, "y", x.dtype)
+    if x.shape != y.shape:
+        raise ValueError("scaled_sum takes two tensors of equal shape")
+    out = torch.empty_like(x)
+    f = _fn("elementwise", f"gllm_scaled_sum_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), y.data_ptr(), out.data_ptr(), float(a), float(b), x.numel(), _stream()), "scaled_sum")
+    return out
+
+
 # --------------------------------------------------- rotary + cache store
 def rope_store(
     qkv: torch.Tensor,
@@ -503,8 +554,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     value per output column) the result is an ordinary tensor with the bias added."""
     if bias is not None:
         return add_bias(linear(x, weight, out_dtype=out_dtype, out=out), bias)
-    _cuda(x, "x")
+    _cuda(x, "x", contiguous=False)             # rows may be a slice of wider rows
     _cuda(weight, "weight", x.dtype)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be [tokens, columns] with contiguous columns")
     m, k = x.shape
     n, k2 = weight.shape
     if k != k2:
@@ -529,7 +582,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         if out_dtype != torch.float32:
             raise TypeError("the fp32 product writes fp32")
         f = _fn("gemm_fp32", "gllm_gemm_f32")
-        _check(f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, k, k, n, _stream()), "gemm_f32")
+        _check(f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), k, n, _stream()), "gemm_f32")
         return out
     from gllm_b200.ops import gemm_bf16
 

@@ -48,6 +48,9 @@ MODULES = {
     "attention_prefill_bf16": "attention_prefill_bf16.cu",
     "attention_prefill_tmem": "attention_prefill_tmem.cu",
     "attention_decode_tma": "attention_decode_tma.cu",
+    "recurrent": "recurrent.cu",
+    "hyper_streams": "hyper_streams.cu",
+    "attention_sigmoid": "attention_sigmoid.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

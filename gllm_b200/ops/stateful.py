@@ -1,0 +1,262 @@
+"""Python entry points of the kernels for mixers that carry a state, for sigmoid-weighted attention
+and for a residual kept as several streams (``csrc/recurrent.cu``, ``csrc/attention_sigmoid.cu``,
+``csrc/hyper_streams.cu``).  As everywhere in ``gllm_b200.ops``: CUDA tensors only, no CPU path.
+
+The batch is the step function's flat batch: request ``r`` owns rows ``cu_q[r] .. cu_q[r+1]-1`` and
+row ``state_slots[r]`` of every state tensor.  States are fp32 and are read and written in place.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix, status_word
+
+
+def _rows(t: torch.Tensor, name: str, dtype=None) -> None:
+    _cuda(t, name, dtype, contiguous=False)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be [tokens, columns] with contiguous columns")
+
+
+# ------------------------------------------------------------------ streams
+def embed_streams(tokens: torch.Tensor, table: torch.Tensor, positions: torch.Tensor | None,
+                  frequencies: torch.Tensor | None, streams: int = 1, sampled: torch.Tensor | None = None,
+                  token_row: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """fp32 ``[n, streams * width]``: ``table[tokens] * scale`` plus, with ``frequencies`` (fp32
+    ``[ceil(width / 2)]``), a sinusoid of the position (column 2i: sin(p f_i), column 2i+1: cos(p f_i)),
+    copied into each of the ``streams`` residual streams.  A negative token id stands for
+    ``sampled[token_row[i]]`` as in ``ops.embedding``."""
+    _cuda(tokens, "tokens", torch.int32)
+    _cuda(table, "table")
+    n, (vocab, width) = tokens.numel(), table.shape
+    if frequencies is not None:
+        _cuda(frequencies, "frequencies", torch.float32)
+        _cuda(positions, "positions", torch.int32)
+        if frequencies.numel() != (width + 1) // 2:
+            raise ValueError("one frequency per pair of columns is needed")
+    if sampled is not None:
+        _cuda(sampled, "sampled", torch.int32)
+        _cuda(token_row, "token_row", torch.int32)
+    out = torch.empty((n, streams * width), dtype=torch.float32, device=table.device)
+    f = _fn("hyper_streams", f"gllm_embed_streams_{_suffix(table.dtype)}")
+    _check(f(tokens.data_ptr(), _ptr(sampled), _ptr(token_row) if sampled is not None else None, table.data_ptr(),
+             _ptr(positions) if frequencies is not None else None, _ptr(frequencies), out.data_ptr(), n, width, vocab,
+             int(streams), float(scale), status_word(table.device).data_ptr(), _stream()), "embed_streams")
+    return out
+
+
+def stream_mix_norm(y: torch.Tensor | None, resid: torch.Tensor, mix: torch.Tensor | None, write: torch.Tensor | None,
+                    read: torch.Tensor | None, weight: torch.Tensor | None, eps: float, out_dtype: torch.dtype,
+                    streams: int, rows: torch.Tensor | None = None, want_norm: bool = True,
+                    want_sum: bool = False):
+    """The write of one sublayer and the read + RMS norm of the next on ``resid [n, streams * width]`` fp32.
+
+    With ``y`` (a sublayer's result ``[n, width]``): every stream becomes
+    ``new[t] = sum_s mix[s, t] * old[s] + write[t] * y`` (in place; with ``rows`` only those tokens are
+    computed and ``resid`` stays as it is).  Then ``u = sum_t read[t] * new[t]`` (``read`` None: the plain
+    sum of the streams) and the result is ``u / sqrt(mean(u^2) + eps) * weight`` in ``out_dtype``; with
+    ``want_sum`` also (or only, ``want_norm`` False) ``u`` itself in fp32."""
+    _cuda(resid, "resid", torch.float32)
+    n, total = resid.shape
+    if total % streams:
+        raise ValueError("the residual's rows do not hold a whole number of streams")
+    width = total // streams
+    if y is not None:
+        _cuda(y, "y", out_dtype)
+        if tuple(y.shape) != (n, width):
+            raise ValueError("the sublayer's result and the residual differ in shape")
+        _cuda(mix, "mix", torch.float32)
+        _cuda(write, "write", torch.float32)
+        if mix.numel() != streams * streams or write.numel() != streams:
+            raise ValueError("mix is [streams, streams] and write is [streams]")
+    if read is not None:
+        _cuda(read, "read", torch.float32)
+        if read.numel() != streams:
+            raise ValueError("read is [streams]")
+    n_rows = n if rows is None else rows.numel()
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+    out = sums = None
+    if want_norm:
+        _cuda(weight, "weight", torch.float32)
+        if weight.numel() != width:
+            raise ValueError("one norm weight per column is needed")
+        out = torch.empty((n_rows, width), dtype=out_dtype, device=resid.device)
+    if want_sum:
+        sums = torch.empty((n_rows, width), dtype=torch.float32, device=resid.device)
+    f = _fn("hyper_streams", f"gllm_stream_mix_norm_{_suffix(out_dtype)}")
+    _check(f(_ptr(y), resid.data_ptr(), _ptr(mix) if y is not None else None, _ptr(write) if y is not None else None,
+             _ptr(read), _ptr(weight) if want_norm else None, _ptr(out), _ptr(sums), _ptr(rows), n_rows, width,
+             int(streams), float(eps), _stream()), "stream_mix_norm")
+    if want_norm and want_sum:
+        return out, sums
+    return out if want_norm else sums
+
+
+# ------------------------------------------------------------------ convolution and scan
+def conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
+              positions: torch.Tensor, token_row: torch.Tensor) -> torch.Tensor:
+    """``silu(causal_conv(x) + bias)`` per channel over each request's own tokens.  ``x [n, channels]``
+    (rows may be a slice of wider rows), ``weight [channels, taps]`` fp32 whose last column multiplies
+    the current token, ``conv_state [slots, taps-1, channels]`` fp32: each request's last ``taps-1``
+    inputs before this step, oldest first (read only; ``selective_scan`` brings it up to date)."""
+    _rows(x, "x")
+    _cuda(weight, "weight", torch.float32)
+    _cuda(conv_state, "conv_state", torch.float32)
+    n, channels = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != channels or tuple(conv_state.shape[1:]) != (max(taps - 1, 0), channels):
+        raise ValueError("conv weight or state does not fit the channels")
+    out = torch.empty((n, channels), dtype=x.dtype, device=x.device)
+    f = _fn("recurrent", f"gllm_conv_silu_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), _ptr(bias), conv_state.data_ptr(), positions.data_ptr(),
+             token_row.data_ptr(), out.data_ptr(), n, channels, taps, _stream()), "conv_silu")
+    return out
+
+
+def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, A: torch.Tensor,
+                   proj: torch.Tensor, b_offset: int, c_offset: int, D: torch.Tensor, xz: torch.Tensor,
+                   z_offset: int, ssm_state: torch.Tensor, conv_state: torch.Tensor, taps: int,
+                   cu_q: torch.Tensor, state_slots: torch.Tensor, num_requests: int) -> torch.Tensor:
+    """Per channel c and state n, token after token of each request:
+    ``dt = softplus(dt_raw + dt_bias)``, ``S[c, n] = exp(dt A[c, n]) S[c, n] + dt x B[n]``,
+    ``y = sum_n S[c, n] C[n] + D[c] x``, result ``y * silu(z)``.  ``B`` and ``C`` are the columns
+    ``b_offset ..`` and ``c_offset ..`` of ``proj``, ``z`` the columns ``z_offset ..`` of ``xz`` whose
+    first columns are the raw (unconvolved) inputs, the last ``taps-1`` of which become the new
+    ``conv_state``.  ``ssm_state [slots, channels, states]`` fp32 is updated in place."""
+    _cuda(xc, "xc")
+    _cuda(dt_raw, "dt_raw", torch.float32)
+    _rows(proj, "proj", xc.dtype)
+    _rows(xz, "xz", xc.dtype)
+    for name, t in (("dt_bias", dt_bias), ("A", A), ("D", D), ("ssm_state", ssm_state), ("conv_state", conv_state)):
+        _cuda(t, name, torch.float32)
+    n, channels = xc.shape
+    n_state = A.shape[1]
+    if tuple(ssm_state.shape[1:]) != (channels, n_state) or tuple(dt_raw.shape) != (n, channels):
+        raise ValueError("the scan's operands do not fit together")
+    out = torch.empty((n, channels), dtype=xc.dtype, device=xc.device)
+    f = _fn("recurrent", f"gllm_selective_scan_{_suffix(xc.dtype)}")
+    _check(f(xc.data_ptr(), dt_raw.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), proj.data_ptr(), proj.stride(0),
+             int(b_offset), int(c_offset), D.data_ptr(), xz.data_ptr(), xz.stride(0), int(z_offset),
+             ssm_state.data_ptr(), conv_state.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), out.data_ptr(),
+             int(num_requests), channels, n_state, int(taps), _stream()), "selective_scan")
+    return out
+
+
+# ------------------------------------------------------------------ matrix recurrences
+GATED_LINEAR = 0      # a = f, b = 1 - f, f = lower + (1 - lower) sigmoid(raw + bias); q = silu(raw q)
+EXP_GATED = 1         # exponential input gate, log-sigmoid forget gate, running maximum, normaliser
+
+
+def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor, gates: torch.Tensor,
+                      gate_bias: torch.Tensor, lower: torch.Tensor | None, cap: float, q_scale: float,
+                      state: torch.Tensor, mstate: torch.Tensor | None, cu_q: torch.Tensor,
+                      state_slots: torch.Tensor, num_requests: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """``S <- diag(a) S + b v^T``, ``o = S^T q`` per (request, head), token after token.
+    ``q, k [n, heads*dk]``, ``v [n, heads*dv]`` (rows may be slices), ``gates`` fp32 (``[n, heads*dk]``
+    in mode ``GATED_LINEAR``, ``[n, 2*heads]`` = input | forget in mode ``EXP_GATED``).  ``state`` is
+    ``[slots, heads, dk, dv]`` (``dv + 1`` columns in mode ``EXP_GATED``: the last carries the
+    normaliser) and ``mstate [slots, heads]`` the running maximum.  Returns fp32
+    ``[n, heads * cols]``: ``cols = dv``, or ``dv + 2`` in mode ``EXP_GATED``, the two extra columns
+    being ``n . q`` and ``exp(-m)``."""
+    _rows(q, "q")
+    _rows(v, "v", q.dtype)
+    if k is not None:
+        _rows(k, "k", q.dtype)
+    _rows(gates, "gates", torch.float32)
+    _cuda(gate_bias, "gate_bias", torch.float32)
+    _cuda(state, "state", torch.float32)
+    n = q.shape[0]
+    extra = 1 if mode == EXP_GATED else 0
+    if tuple(state.shape[1:]) != (heads, dk, dv + extra):
+        raise ValueError("the recurrence's state does not fit its heads")
+    if mode == EXP_GATED:
+        _cuda(mstate, "mstate", torch.float32)
+        if k is None or gates.shape[1] != 2 * heads:
+            raise ValueError("the exponential-gate recurrence takes keys and two gates per head")
+    else:
+        _cuda(lower, "lower", torch.float32)
+    cols = dv + 2 * extra
+    out = torch.empty((n, heads * cols), dtype=torch.float32, device=q.device)
+    f = _fn("recurrent", f"gllm_matrix_recurrence_{_suffix(q.dtype)}")
+    _check(f(int(mode), q.data_ptr(), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, v.data_ptr(),
+             v.stride(0), gates.data_ptr(), gates.stride(0), gate_bias.data_ptr(), _ptr(lower), float(cap),
+             float(q_scale), state.data_ptr(), _ptr(mstate), cu_q.data_ptr(), state_slots.data_ptr(),
+             out.data_ptr(), out.stride(0), int(num_requests), heads, dk, dv, _stream()), "matrix_recurrence")
+    return out
+
+
+def head_norm(o: torch.Tensor, heads: int, dv: int, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              with_denominator: bool = False, denominator_eps: float = 0.0,
+              gate: torch.Tensor | None = None) -> torch.Tensor:
+    """Each head of ``o`` (fp32 ``[n, heads * cols]`` as ``matrix_recurrence`` returns it) divided by
+    its root mean square over its ``dv`` values, times ``weight`` (``[dv]``: shared by the heads;
+    ``[heads * dv]``: one per column), times ``sigmoid(gate)`` when given.  ``with_denominator``: the
+    head is first divided by ``max(|o[dv]|, o[dv+1]) + denominator_eps``."""
+    _cuda(o, "o", torch.float32)
+    _cuda(weight, "weight", torch.float32)
+    n = o.shape[0]
+    cols = o.shape[1] // heads
+    if weight.numel() not in (dv, heads * dv) or cols < dv + (2 if with_denominator else 0):
+        raise ValueError("head_norm's operands do not fit together")
+    if gate is not None:
+        _rows(gate, "gate", out_dtype)
+    out = torch.empty((n, heads * dv), dtype=out_dtype, device=o.device)
+    f = _fn("recurrent", f"gllm_head_norm_{_suffix(out_dtype)}")
+    _check(f(o.data_ptr(), o.stride(0), cols, int(with_denominator), float(denominator_eps), weight.data_ptr(),
+             dv if weight.numel() == heads * dv and heads > 1 else 0, _ptr(gate),
+             gate.stride(0) if gate is not None else 0, out.data_ptr(), out.stride(0), n, heads, dv, float(eps),
+             _stream()), "head_norm")
+    return out
+
+
+# ------------------------------------------------------------------ sigmoid attention
+def qk_norm_store(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Tensor, eps: float, temp_coef: float,
+                  temp_every: float, positions: torch.Tensor, slot_mapping: torch.Tensor | None,
+                  cache_pages: torch.Tensor | None, heads: int, kv_heads: int, dk: int, dv: int,
+                  block_size: int) -> torch.Tensor:
+    """In place on ``qkv [n, heads*dk + kv_heads*dk + kv_heads*dv]``: RMS norm of every query and key
+    head (weights ``[dk]``), queries times ``1 + temp_coef * ln(floor((p+1) / temp_every) + 1)``; the
+    normed keys and the values go into ``cache_pages [pages, block_size * kv_heads * (dk + dv)]`` at
+    ``slot_mapping``."""
+    _cuda(qkv, "qkv")
+    _cuda(q_weight, "q_weight", torch.float32)
+    _cuda(k_weight, "k_weight", torch.float32)
+    n = qkv.shape[0]
+    if qkv.shape[1] != heads * dk + kv_heads * (dk + dv) or q_weight.numel() != dk or k_weight.numel() != dk:
+        raise ValueError("qkv width or the norm weights do not fit the heads")
+    num_pages = 0
+    if slot_mapping is not None:
+        _cuda(slot_mapping, "slot_mapping", torch.int32)
+        _cuda(cache_pages, "cache_pages", qkv.dtype)
+        num_pages = cache_pages.shape[0]
+        if cache_pages.shape[1] != block_size * kv_heads * (dk + dv):
+            raise ValueError("the cache pages do not hold keys and values of these widths")
+    f = _fn("attention_sigmoid", f"gllm_qk_norm_store_{_suffix(qkv.dtype)}")
+    _check(f(qkv.data_ptr(), qkv.stride(0), q_weight.data_ptr(), k_weight.data_ptr(), float(eps), float(temp_coef),
+             float(temp_every), positions.data_ptr(), _ptr(slot_mapping),
+             _ptr(cache_pages) if slot_mapping is not None else None, n, heads, kv_heads, dk, dv, int(block_size),
+             num_pages, status_word(qkv.device).data_ptr(), _stream()), "qk_norm_store")
+    return qkv
+
+
+def sigmoid_attention(qkv: torch.Tensor, cache_pages: torch.Tensor, block_table: torch.Tensor,
+                      positions: torch.Tensor, token_row: torch.Tensor, head_bias: torch.Tensor | None, heads: int,
+                      kv_heads: int, dk: int, dv: int, block_size: int, scale: float) -> torch.Tensor:
+    """``out[i, h] = sum_{j <= p_i} sigmoid(q . k_j * scale + head_bias[h]) v_j`` over the request's
+    cached keys and values (this step's own included); queries are the first ``heads * dk`` columns of
+    ``qkv``.  Returns ``[n, heads * dv]``."""
+    _cuda(qkv, "qkv")
+    _cuda(cache_pages, "cache_pages", qkv.dtype)
+    _cuda(block_table, "block_table", torch.int32, contiguous=False)
+    if head_bias is not None:
+        _cuda(head_bias, "head_bias", torch.float32)
+    n = qkv.shape[0]
+    out = torch.empty((n, heads * dv), dtype=qkv.dtype, device=qkv.device)
+    f = _fn("attention_sigmoid", f"gllm_attention_sigmoid_{_suffix(qkv.dtype)}")
+    _check(f(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), cache_pages.data_ptr(),
+             block_table.data_ptr(), block_table.stride(0), positions.data_ptr(), token_row.data_ptr(),
+             _ptr(head_bias), n, heads, kv_heads, dk, dv, int(block_size), cache_pages.shape[0], float(scale),
+             status_word(qkv.device).data_ptr(), _stream()), "sigmoid_attention")
+    return out

@@ -25,7 +25,9 @@ from gllm_b200.parts.base import (
     register_norm,
     register_position_encoding,
 )
-from gllm_b200.parts import attention, block, mlp, norm, rotary  # noqa: F401  (register the built-in kinds)
+from gllm_b200.parts import (  # noqa: F401  (register the built-in kinds)
+    attention, block, hyper, mamba, matrix_memory, mlp, norm, parallel, rotary, sigmoid_attention,
+)
 
 __all__ = [
     "BLOCKS", "FEED_FORWARDS", "MIXERS", "NORMS", "POSITION_ENCODINGS",

@@ -35,7 +35,8 @@ class TensorExpectation:
     role "matrix": operand of a matrix product or an embedding table, held in
     the compute dtype.  "vector": small per-channel tensor (norm weight), held
     in fp32 whatever the compute dtype is.  "bias": the bias of a projection, held in fp32
-    as well (random weights draw it around zero, a vector around one).  "int_table": integer table, int32.
+    as well (random weights draw it around zero, a vector around one).  "mixing": a small square matrix
+    that mixes parallel streams, fp32 (random weights draw it around the identity).  "int_table": integer table, int32.
     """
 
     shape: tuple[int, ...]
@@ -141,6 +142,8 @@ class MixerCache:
     state: torch.Tensor | None = None     # [max_batch_size + 1, *StateRequirement.shape]; last row: padding rows
     requirement: KVPageRequirement | None = None
     block_size: int = 0
+    # every state tensor the mixer declared, in its order (``state`` is the first of them)
+    states: tuple = ()
 
     def tensor(self, index: int) -> torch.Tensor:
         """The ``index``-th tensor the mixer declared, as a view ``[pages, heads, block_size, width]``
@@ -217,7 +220,9 @@ class Mixer(Part):
     def kv_requirement(self) -> KVPageRequirement | None:
         return None
 
-    def state_requirement(self) -> StateRequirement | None:
+    def state_requirement(self) -> "StateRequirement | tuple[StateRequirement, ...] | None":
+        """One fixed-size tensor per live request, or several (a tuple): a scan's state beside the
+        last inputs of its convolution, a matrix memory beside its running maximum."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: MixerCache) -> torch.Tensor:
@@ -241,16 +246,19 @@ class Block(Part):
     mixer that asks for a cache (the plan gives every entry one cache)."""
 
     part_kinds: dict[str, str] = {}
+    # names of ``part_kinds`` that a layer may leave out (a layer without a feed-forward): the
+    # attribute is then None
+    optional_parts: frozenset = frozenset()
 
     def __init__(self, **parts: Part):
         super().__init__()
-        missing = [n for n in self.part_kinds if n not in parts]
+        missing = [n for n in self.part_kinds if n not in parts and n not in self.optional_parts]
         extra = [n for n in parts if n not in self.part_kinds]
         if missing or extra:
             raise ValueError(f"block {type(self).__name__}: missing parts {missing}, unexpected parts {extra}")
-        self._part_names = list(self.part_kinds)
-        for name in self._part_names:
-            setattr(self, name, parts[name])
+        self._part_names = [n for n in self.part_kinds if n in parts]
+        for name in self.part_kinds:
+            setattr(self, name, parts.get(name))
 
     def parts(self) -> list[Part]:
         return [getattr(self, n) for n in self._part_names]

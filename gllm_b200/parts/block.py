@@ -17,13 +17,16 @@ from gllm_b200.parts.base import Block, register_block
 class PreNormBlock(Block):
     graph_safe_portions = True
     part_kinds = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+    # a layer may have a mixer only
+    optional_parts = frozenset({"feed_forward_norm", "feed_forward"})
 
     def forward(self, branch, resid, ctx, cache):
         # a part may add its result into the residual itself (its last product's epilogue) and say so
         ctx.residual_sink = resid
         x = self.mixer_norm.forward(None if branch is ops.ADDED else branch, resid, ctx.dtype)
-        mixed = self.mixer.forward(x, ctx, cache)
-        x = self.feed_forward_norm.forward(None if mixed is ops.ADDED else mixed, resid, ctx.dtype)
-        out = self.feed_forward.forward(x, ctx)
+        out = self.mixer.forward(x, ctx, cache)
+        if self.feed_forward is not None:
+            x = self.feed_forward_norm.forward(None if out is ops.ADDED else out, resid, ctx.dtype)
+            out = self.feed_forward.forward(x, ctx)
         ctx.residual_sink = None
         return out, resid

@@ -1,0 +1,71 @@
+"""Selective state-space mixer (Mamba's first form).
+
+``[x | z] = W_in h``; ``x`` passes a short causal convolution per channel (with bias) and SiLU;
+``[dt | B | C] = W_x x``; ``dt = softplus(W_dt dt + b)`` per channel; ``A = -exp(A_log)``;
+``S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n``, ``y_c = sum_n S[c, n] C_n + D_c x_c``; the
+result is ``W_o (y * silu(z))``.  Per request it keeps the scan state ``[inner, states]`` and the
+convolution's last ``taps - 1`` inputs, both fp32; step sizes, decays and the state are fp32 whatever
+the activations' type.  The products run on the engine's product kernels, the convolution and the scan
+on ``csrc/recurrent.cu``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.ops import stateful
+from gllm_b200.parts.base import Mixer, StateRequirement, TensorExpectation, register_mixer
+
+
+@register_mixer("selective_scan")
+class SelectiveScanMixer(Mixer):
+    graph_safe_portions = True
+
+    def __init__(self, names, hidden_size: int, inner: int, states: int, dt_rank: int, taps: int):
+        super().__init__(names)
+        self.hidden_size, self.inner, self.n_state = int(hidden_size), int(inner), int(states)
+        self.dt_rank, self.taps = int(dt_rank), int(taps)
+        if not 1 <= self.taps <= 16 or self.n_state > 256:
+            raise ValueError("the scan kernels take 1..16 convolution taps and up to 256 states per channel")
+        self.w_in = self.w_x = self.w_dt = self.w_o = None
+        self.conv_w = self.conv_b = self.dt_b = self.A = self.D = None
+
+    def kernel_needs(self):
+        return {"modules": {"recurrent"}}
+
+    def state_requirement(self):
+        return (StateRequirement((self.inner, self.n_state), torch.float32),
+                StateRequirement((max(self.taps - 1, 0), self.inner), torch.float32))
+
+    def expected_tensors(self):
+        n = self.names
+        return {
+            n["in"]: TensorExpectation((2 * self.inner, self.hidden_size)),
+            n["conv"]: TensorExpectation((self.inner, self.taps), "vector"),
+            n["conv_bias"]: TensorExpectation((self.inner,), "bias"),
+            n["x"]: TensorExpectation((self.dt_rank + 2 * self.n_state, self.inner)),
+            n["dt"]: TensorExpectation((self.inner, self.dt_rank)),
+            n["dt_bias"]: TensorExpectation((self.inner,), "bias"),
+            n["A_log"]: TensorExpectation((self.inner, self.n_state), "vector"),
+            n["D"]: TensorExpectation((self.inner,), "vector"),
+            n["o"]: TensorExpectation((self.hidden_size, self.inner)),
+        }
+
+    def load(self, get, dtype, device):
+        n = self.names
+        self.w_in, self.w_x, self.w_dt, self.w_o = (get(n[k], "matrix") for k in ("in", "x", "dt", "o"))
+        self.conv_w, self.conv_b = get(n["conv"], "vector"), get(n["conv_bias"], "bias")
+        self.dt_b, self.D = get(n["dt_bias"], "bias"), get(n["D"], "vector")
+        self.A = (-torch.exp(get(n["A_log"], "vector"))).contiguous()
+
+    def forward(self, x, ctx, cache):
+        ssm_state, conv_state = cache.states
+        xz = ops.linear(x, self.w_in)
+        xc = stateful.conv_silu(xz[:, : self.inner], self.conv_w, self.conv_b, conv_state, ctx.positions, ctx.token_row)
+        proj = ops.linear(xc, self.w_x)
+        dt_raw = ops.linear(proj[:, : self.dt_rank], self.w_dt, out_dtype=torch.float32)
+        y = stateful.selective_scan(xc, dt_raw, self.dt_b, self.A, proj, self.dt_rank, self.dt_rank + self.n_state,
+                                    self.D, xz, self.inner, ssm_state, conv_state, self.taps, ctx.cu_q,
+                                    ctx.state_slots, ctx.num_requests)
+        return ops.linear(y, self.w_o, split_ok=True, add_into=getattr(ctx, "residual_sink", None))

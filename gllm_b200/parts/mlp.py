@@ -63,3 +63,32 @@ class SwiGLU(FeedForward):
         else:
             hidden = ops.silu_mul(ops.linear(x, self.w_gate_up, bias=self.b_gate_up))
         return ops.linear(hidden, self.w_down, split_ok=True, add_into=sink, bias=self.b_down)
+
+
+@register_feed_forward("dense")
+class DenseFeedForward(FeedForward):
+    """``down(act(up(x)))`` without a gate.  ``activation`` "relu_squared": ``max(z, 0) ** 2``."""
+
+    graph_safe_portions = True
+    ACTIVATIONS = {"relu_squared": ops.relu_sq}
+
+    def __init__(self, names, hidden_size: int, intermediate_size: int, activation: str = "relu_squared"):
+        super().__init__(names)
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unknown activation {activation!r}; known: {sorted(self.ACTIVATIONS)}")
+        self.hidden_size, self.intermediate_size, self.activation = int(hidden_size), int(intermediate_size), activation
+        self.w_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+
+    def expected_tensors(self):
+        return {
+            self.names["up"]: TensorExpectation((self.intermediate_size, self.hidden_size)),
+            self.names["down"]: TensorExpectation((self.hidden_size, self.intermediate_size)),
+        }
+
+    def load(self, get, dtype, device):
+        self.w_up, self.w_down = get(self.names["up"], "matrix"), get(self.names["down"], "matrix")
+
+    def forward(self, x, ctx):
+        hidden = self.ACTIVATIONS[self.activation](ops.linear(x, self.w_up))
+        return ops.linear(hidden, self.w_down, split_ok=True, add_into=getattr(ctx, "residual_sink", None))

@@ -46,6 +46,8 @@ def random_tensors(
             t = torch.ones(exp.shape, dtype=torch.float32)
             if norm_jitter:
                 t = t + torch.randn(exp.shape, generator=gen, dtype=torch.float32) * norm_jitter
+        elif exp.role == "mixing":
+            t = torch.eye(exp.shape[0], dtype=torch.float32) + torch.randn(exp.shape, generator=gen, dtype=torch.float32) * std
         elif exp.role in ("matrix", "bias"):
             s = std
             for pattern, value in (std_overrides or {}).items():
