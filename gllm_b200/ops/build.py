@@ -51,6 +51,7 @@ MODULES = {
     "recurrent": "recurrent.cu",
     "hyper_streams": "hyper_streams.cu",
     "attention_sigmoid": "attention_sigmoid.cu",
+    "attention_sigmoid_mma": "attention_sigmoid_mma.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -8,9 +8,14 @@ row ``state_slots[r]`` of every state tensor.  States are fp32 and are read and 
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix, status_word
+
+# GLLM_B200_SIGMOID_MMA=0: the sigmoid attention of bf16 models stays on the CUDA-core kernel (for measurements)
+USE_TENSOR_CORES = os.environ.get("GLLM_B200_SIGMOID_MMA", "1") != "0"
 
 
 def _rows(t: torch.Tensor, name: str, dtype=None) -> None:
@@ -241,12 +246,73 @@ def qk_norm_store(qkv: torch.Tensor, q_weight: torch.Tensor, k_weight: torch.Ten
     return qkv
 
 
+_mma = None
+SPLIT_KEYS = 256          # keys per CTA when single tokens' contexts are cut (a multiple of the key tile of 64)
+MAX_SPLITS = 16           # what the kernel that adds the partial results takes
+
+
+def _mma_fns():
+    global _mma
+    if _mma is None:
+        from ctypes import c_float, c_int, c_int64, c_void_p as P
+
+        from gllm_b200.ops.build import load_module
+
+        lib = load_module("attention_sigmoid_mma")
+        f = lib.gllm_attention_sigmoid_mma
+        f.argtypes = [P, c_int64, P, c_int64, P, c_int64, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_int, c_float, c_int, c_int, P, P]
+        f.restype = c_int
+        lib.gllm_attention_sigmoid_mma_supports.argtypes = [c_int, c_int]
+        lib.gllm_attention_sigmoid_mma_tokens_per_tile.argtypes = [c_int, c_int]
+        _mma = (f, lib.gllm_attention_sigmoid_mma_supports, lib.gllm_attention_sigmoid_mma_tokens_per_tile)
+    return _mma
+
+
+def sigmoid_attention_takes_tensor_cores(dtype: torch.dtype, dk: int, dv: int) -> bool:
+    """True for the sizes the tensor-core kernel is built for (bf16; widths 32, 64, 96 or 128)."""
+    return dtype == torch.bfloat16 and all(d in (32, 64, 96, 128) for d in (dk, dv))
+
+
+def _sigmoid_attention_mma(qkv, cache_pages, block_table, head_bias, heads, kv_heads, dk, dv, block_size, scale, batch, out):
+    """The tensor-core kernel.  Steps whose tiles do not fill the GPU (single tokens over long contexts)
+    cut every request's keys into ranges of at least ``SPLIT_KEYS`` keys, one CTA each; the partial results are
+    added in ascending order."""
+    from gllm_b200 import ops
+
+    f, _, tokens_per_tile = _mma_fns()
+    n = qkv.shape[0]
+    qt = tokens_per_tile(heads, kv_heads)
+    group = heads // kv_heads
+    head_tiles = kv_heads * (group if 64 % group or group > 64 else 1)
+    tiles = -(-batch.max_q_len // qt) * head_tiles * batch.num_requests
+    sms = torch.cuda.get_device_properties(qkv.device).multi_processor_count
+    splits, tiles_per_split = 1, 0
+    if tiles < sms and batch.max_seq_len > 2 * SPLIT_KEYS:
+        want = min(MAX_SPLITS, -(-2 * sms // tiles))
+        tiles_per_split = max(SPLIT_KEYS // 64, -(-(-(-batch.max_seq_len // 64)) // want))
+        splits = -(-(-(-batch.max_seq_len // 64)) // tiles_per_split)
+    partial = None
+    if splits > 1:
+        partial = batch.workspace.get("sigmoid_attention_partial", splits * n * heads * dv, torch.float32)
+    code = f(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), _ptr(partial), n * heads * dv,
+             cache_pages.data_ptr(), block_table.data_ptr(), block_table.stride(0), batch.cu_q.data_ptr(),
+             batch.context_lens.data_ptr(), batch.state_slots.data_ptr(), _ptr(head_bias), batch.num_requests,
+             batch.max_q_len, heads, kv_heads, dk, dv, int(block_size), cache_pages.shape[0], float(scale), splits,
+             tiles_per_split, status_word(qkv.device).data_ptr(), _stream())
+    _check(code, "sigmoid_attention_mma")
+    if splits > 1:
+        ops.SplitSum(partial.view(splits, n, heads * dv), out.dtype).tensor(out)
+    return out
+
+
 def sigmoid_attention(qkv: torch.Tensor, cache_pages: torch.Tensor, block_table: torch.Tensor,
                       positions: torch.Tensor, token_row: torch.Tensor, head_bias: torch.Tensor | None, heads: int,
-                      kv_heads: int, dk: int, dv: int, block_size: int, scale: float) -> torch.Tensor:
+                      kv_heads: int, dk: int, dv: int, block_size: int, scale: float, batch=None) -> torch.Tensor:
     """``out[i, h] = sum_{j <= p_i} sigmoid(q . k_j * scale + head_bias[h]) v_j`` over the request's
     cached keys and values (this step's own included); queries are the first ``heads * dk`` columns of
-    ``qkv``.  Returns ``[n, heads * dv]``."""
+    ``qkv``.  Returns ``[n, heads * dv]``.  With ``batch`` (the StepContext: per-request lengths and slots) bf16
+    inputs of the sizes it takes run on the tensor-core kernel, everything else on the CUDA cores in fp32."""
     _cuda(qkv, "qkv")
     _cuda(cache_pages, "cache_pages", qkv.dtype)
     _cuda(block_table, "block_table", torch.int32, contiguous=False)
@@ -254,6 +320,10 @@ def sigmoid_attention(qkv: torch.Tensor, cache_pages: torch.Tensor, block_table:
         _cuda(head_bias, "head_bias", torch.float32)
     n = qkv.shape[0]
     out = torch.empty((n, heads * dv), dtype=qkv.dtype, device=qkv.device)
+    if (batch is not None and sigmoid_attention_takes_tensor_cores(qkv.dtype, dk, dv) and qkv.stride(0) % 8 == 0
+            and (block_size * dk) % 8 == 0 and USE_TENSOR_CORES):
+        return _sigmoid_attention_mma(qkv, cache_pages, block_table, head_bias, heads, kv_heads, dk, dv, block_size,
+                                      scale, batch, out)
     f = _fn("attention_sigmoid", f"gllm_attention_sigmoid_{_suffix(qkv.dtype)}")
     _check(f(qkv.data_ptr(), qkv.stride(0), out.data_ptr(), out.stride(0), cache_pages.data_ptr(),
              block_table.data_ptr(), block_table.stride(0), positions.data_ptr(), token_row.data_ptr(),

@@ -35,7 +35,7 @@ class SigmoidAttention(Mixer):
         self.w_qkv = self.w_o = self.q_norm = self.k_norm = self.head_bias = None
 
     def kernel_needs(self):
-        return {"modules": {"attention_sigmoid"}}
+        return {"modules": {"attention_sigmoid", "attention_sigmoid_mma"}}
 
     def kv_requirement(self):
         return KVPageRequirement(((self.kv_heads, self.dk), (self.kv_heads, self.dv)), None)
@@ -67,5 +67,5 @@ class SigmoidAttention(Mixer):
                                self.dk, self.dv, cache.block_size)
         attn = stateful.sigmoid_attention(qkv, cache.pages, view.block_table, ctx.positions, ctx.token_row,
                                           self.head_bias, self.heads, self.kv_heads, self.dk, self.dv, cache.block_size,
-                                          self.scale)
+                                          self.scale, batch=ctx)
         return ops.linear(attn, self.w_o, split_ok=True, add_into=getattr(ctx, "residual_sink", None))

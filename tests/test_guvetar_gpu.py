@@ -17,7 +17,7 @@ from tiny_guvetar import GUVETAR, draw_weights, single_mixer, write_model
 
 pytestmark = pytest.mark.gpu
 
-PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 16, "E": 16}
 
 
 def tolerance(dtype):
@@ -62,7 +62,7 @@ def test_each_mixer_alone(kind, streams, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_all_cuts_and_mixed_batches(name, dtype, tmp_path):
     cfg = GUVETAR[name]
     weights, _, runner = make(cfg, tmp_path, dtype, max_tokens=rounded(max(LENGTHS.values())), block_size=PAGE[name])
@@ -114,7 +114,7 @@ def far_key_model():
     cfg = single_mixer("sigmoid_only")
     cfg = copy.deepcopy(cfg)
     left = cfg["layers"][0]["mixer"]["left"]
-    left["scale"] = 0.5
+    left["scale"], left["heads"], left["kv_heads"] = 0.5, 1, 1
     w = draw_weights(cfg, seed=11, sharp=1.0)
     W, d = cfg["width"], left["dim"]
     ca, cb = W - 2, W - 4                       # two slow sine columns: the position adds next to nothing there
@@ -133,6 +133,8 @@ def far_key_model():
     w["l0.mix.left.k.norm"][:] = 1.5
     w["l0.mix.left.pb"][:] = -12.0
     w["l0.mix.left.v"] *= 3.0
+    w["l0.mix.left.o"] *= 2.0
+    w["final.norm"][[ca, cb]] = 0.0           # the two marker columns do not reach the logits themselves
     return cfg, {k: v.to(torch.bfloat16).to(torch.float32) for k, v in w.items()}
 
 
@@ -155,7 +157,7 @@ def test_a_far_key_at_page_and_block_edges(dtype, tmp_path):
         blind = plain_forward(cfg, weights, without)
         scale = max(1.0, float(plain.abs().max()))
         # the test is sharp: losing that one key moves the last logits by far more than the tolerance
-        assert float((plain[-1] - blind[-1]).abs().max()) > (20 if dtype == "float32" else 2) * tol_max * scale
+        assert float((plain[-1] - blind[-1]).abs().max()) > (20 if dtype == "float32" else 4) * tol_max * scale
         # the last token in a portion, and decoded alone
         for cuts in ([n], [n - 1, 1], [far + 1, n - far - 3, 2] if far + 3 < n else [n]):
             steps, index = steps_of(toks, cuts)
@@ -176,6 +178,29 @@ def test_first_tokens_and_long_decoding(dtype, tmp_path):
         steps, index = steps_of(toks, [first] + [1] * (n - first))
         compare(run_steps(runner, steps), index, plain, *tolerance(dtype))
     assert runner.graph_replays > 300
+
+
+def test_single_tokens_over_a_long_context_on_the_tensor_cores(tmp_path):
+    """bfloat16 with head widths the tensor-core attention takes: a context of 900 tokens, then single tokens
+    whose keys are cut into ranges with one CTA each (the partial results are added afterwards), alone and two
+    requests at once; then the same tokens through the CUDA-core kernel agree with them."""
+    cfg = GUVETAR["E"]
+    weights, folder, runner = make(cfg, tmp_path, "bfloat16", max_tokens=2048)
+    g = torch.Generator().manual_seed(31)
+    a = torch.randint(0, cfg["vocab"], (930,), generator=g).tolist()
+    b = torch.randint(0, cfg["vocab"], (700,), generator=g).tolist()
+    plain = {"a": plain_forward(cfg, weights, a), "b": plain_forward(cfg, weights, b)}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:900], "want": [899]}], "end": []},
+             {"step": 1, "entries": [{"id": "b", "tokens": b[:690], "want": [689]}], "end": []}]
+    index = [(0, 0, "a", 899), (1, 0, "b", 689)]
+    for i in range(10):
+        steps.append({"step": 2 + i, "entries": [{"id": "a", "tokens": [a[900 + i]], "want": [0]},
+                                                  {"id": "b", "tokens": [b[690 + i]], "want": [0]}], "end": []})
+        index += [(2 + i, 0, "a", 900 + i), (2 + i, 1, "b", 690 + i)]
+    for i in range(10, 30):
+        steps.append({"step": 2 + i, "entries": [{"id": "a", "tokens": [a[900 + i]], "want": [0]}], "end": []})
+        index.append((2 + i, 0, "a", 900 + i))
+    compare(run_steps(runner, steps), index, plain, BF16_TOL_MAX, BF16_TOL_MEAN)
 
 
 def test_a_slot_and_its_pages_used_again_start_clean(tmp_path):

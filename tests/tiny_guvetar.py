@@ -75,7 +75,22 @@ GUVETAR_D = {
     "architecture": "Guvetar", "vocab": 150, "width": 32, "streams": 4, "norm": {"eps": 1e-5},
     "layers": [_layer(_mlstm(4, 8, 8, 8.0), 48), _layer(_mamba(64, 4, 2, 4), None)],
 }
-GUVETAR = {"A": GUVETAR_A, "B": GUVETAR_B, "C": GUVETAR_C, "D": GUVETAR_D}
+# head widths the tensor-core attention kernel of bfloat16 runs takes (32, 64, 96, 128), with groups of two and
+# of three query heads per key head, beside a scan
+GUVETAR_E = {
+    "architecture": "Guvetar", "vocab": 120, "width": 64, "streams": 2, "norm": {"eps": 1e-5},
+    "layers": [
+        _layer(_parallel({"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 64, "scale": 0.2,
+                          "q_temp": {"coef": 0.3, "every": 7}},
+                         {"heads": 2, "dim": 16, "vdim": 16}, 1.0, 1.0), 64),
+        _layer(_mamba(64, 8, 8, 4), None),
+        _layer(_parallel({"heads": 3, "kv_heads": 1, "dim": 96, "vdim": 32, "scale": 0.12},
+                         {"heads": 1, "dim": 32, "vdim": 32}, 0.6, 0.9), 96),
+        _layer(_parallel({"heads": 2, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.1},
+                         {"heads": 2, "dim": 8, "vdim": 8}, 1.1, 0.3), None),
+    ],
+}
+GUVETAR = {"A": GUVETAR_A, "B": GUVETAR_B, "C": GUVETAR_C, "D": GUVETAR_D, "E": GUVETAR_E}
 
 
 def single_mixer(kind: str, streams=None) -> dict:
@@ -85,7 +100,7 @@ def single_mixer(kind: str, streams=None) -> dict:
         "mlstm": _mlstm(2, 12, 20, 12.0),
         "parallel": _parallel({"heads": 2, "kv_heads": 1, "dim": 12, "vdim": 20, "scale": 0.4,
                                "q_temp": {"coef": 0.5, "every": 3}}, {"heads": 2, "dim": 6, "vdim": 10}, 0.9, 0.6),
-        "sigmoid_only": _parallel({"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 8, "scale": 0.35},
+        "sigmoid_only": _parallel({"heads": 2, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.35},
                                   {"heads": 1, "dim": 4, "vdim": 4}, 1.0, 0.0),
         "hgrn2_only": _parallel({"heads": 1, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 0.3},
                                 {"heads": 3, "dim": 10, "vdim": 14}, 0.0, 1.0),
