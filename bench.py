@@ -486,6 +486,88 @@ def run_scenario(args) -> dict:
     }
 
 
+# ------------------------------------------------------------------ another design beside the closest Llama
+# `--design guvetar`: prefill and decode throughput of Guvetar models at layer sizes of real models (random
+# weights), each beside a Llama of the same width, feed-forward width, layer count and vocabulary.
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, ff=8192, layers=6, vocab=32000, heads=32, kv_heads=8, head_dim=64, inner=4096, state=16,
+                  dt_rank=128, memory_heads=8, memory_dim=128, memory_vdim=256, linear_heads=16, linear_dim=64,
+                  linear_vdim=128),
+    "w1024": dict(width=1024, ff=4096, layers=6, vocab=32000, heads=16, kv_heads=4, head_dim=64, inner=2048, state=16,
+                  dt_rank=64, memory_heads=4, memory_dim=128, memory_vdim=256, linear_heads=8, linear_dim=64,
+                  linear_vdim=128),
+}
+
+
+def guvetar_raw(sz: dict) -> dict:
+    mamba = {"type": "mamba1", "mixer": {"inner": sz["inner"], "state": sz["state"], "dt_rank": sz["dt_rank"], "conv": 4}}
+    memory = {"type": "mlstm", "mixer": {"heads": sz["memory_heads"], "dim": sz["memory_dim"], "vdim": sz["memory_vdim"],
+                                         "gate_cap": 15.0}}
+    pair = {"type": "parallel", "mixer": {
+        "left": {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["head_dim"], "vdim": sz["head_dim"],
+                 "scale": sz["head_dim"] ** -0.5, "q_temp": {"coef": 0.5, "every": 64}},
+        "right": {"heads": sz["linear_heads"], "dim": sz["linear_dim"], "vdim": sz["linear_vdim"]},
+        "left_scale": 0.5, "right_scale": 0.5}}
+    kinds = [mamba, memory, pair]
+    layers = [{**kinds[i % 3], "mlp": {"kind": "dense", "ff": sz["ff"]}} for i in range(sz["layers"])]
+    return {"architecture": "Guvetar", "vocab": sz["vocab"], "width": sz["width"], "streams": 4, "norm": {"eps": 1e-5},
+            "layers": layers, "torch_dtype": "bfloat16"}
+
+
+def llama_raw(sz: dict) -> dict:
+    return dict(architectures=["LlamaForCausalLM"], hidden_size=sz["width"], head_dim=sz["head_dim"],
+                intermediate_size=sz["ff"], hidden_act="silu", num_hidden_layers=sz["layers"],
+                num_attention_heads=sz["heads"], num_key_value_heads=sz["kv_heads"], rms_norm_eps=1e-5, eos_token_id=[0],
+                torch_dtype="bfloat16", rope_theta=10000.0, vocab_size=sz["vocab"], tie_word_embeddings=True)
+
+
+def run_design(args) -> dict:
+    import torch
+
+    from gllm_b200 import GeneratorParams, LLMEngine
+    from gllm_b200.config import load_config
+    from gllm_b200.weights import write_random_model
+
+    context, prefill_tokens = 2048, 2048
+    steps = min(args.steps, 64)
+    rows = {}
+    sampler = ClockSampler(0)
+    sampler.start()
+    for name, sz in DESIGN_SIZES.items():
+        if args.layers:
+            sz = dict(sz, layers=args.layers)
+        rows[name] = {"sizes": sz}
+        for arm, raw in (("guvetar", guvetar_raw(sz)), ("llama", llama_raw(sz))):
+            tmp = tempfile.mkdtemp(prefix="gllm_b200_bench_")
+            try:
+                folder = write_random_model(os.path.join(tmp, arm), load_config(raw), seed=0, std=0.02)
+                params = GeneratorParams(block_size=16, max_batch_size=8, max_seq_len=4096, model_dtype="bfloat16",
+                                         max_num_batched_tokens=8192, prefill_chunk=2048)
+                engine = LLMEngine(folder, params, device="cuda:0")
+            finally:
+                shutil.rmtree(tmp, ignore_errors=True)
+            out = {}
+            pf_ms, pf_e2e = time_prefill(engine, prefill_tokens, repeats=3, warmup=3)
+            out["prefill_tokens_per_s"] = round(prefill_tokens * 1000.0 / pf_ms, 1)
+            out["prefill_ms"] = round(pf_ms, 3)
+            for b in (1, 8):
+                dev_ms, wall_ms, launches, _, _ = time_decode(engine, b, context, steps, max(3, args.warmup), reps=3)
+                out[f"decode_b{b}_tokens_per_s"] = round(b * 1000.0 / dev_ms, 1)
+                out[f"decode_b{b}_ms"] = round(dev_ms, 4)
+                out[f"decode_b{b}_launches"] = round(launches, 1)
+            rows[name][arm] = out
+            del engine
+            torch.cuda.empty_cache()
+    clocks = sampler.stop()
+    return {
+        "metric": "prefill (2,048 tokens) and decode (batch 1 and 8, 2,048 cached tokens) throughput of Guvetar beside a "
+                  "Llama of equal width, feed-forward width, layers and vocabulary (random bf16 weights)",
+        "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "higher_is_better": True,
+        "data": "synthetic: uniform random token ids, random weights (seed 0)",
+        "steps": steps, "warmup": max(3, args.warmup), "rows": rows, "clocks": clocks,
+    }
+
+
 def run_reference(args) -> dict:
     sys.path.insert(0, ROOT)
     from baseline import reference_arm
@@ -515,6 +597,8 @@ def main() -> int:
     ap.add_argument("--shape", default="", help="with --kernel: overrides such as batch=8,context=2048")
     ap.add_argument("--preset", default=None, choices=sorted(SCENARIOS),
                     help="a whole-engine scenario at another model size (a line of its own, not the headline)")
+    ap.add_argument("--design", default=None, choices=["guvetar"],
+                    help="another design's prefill and decode throughput beside the closest Llama (a line of its own)")
     args = ap.parse_args()
     if args.kernel:
         from gllm_b200 import kernel_bench
@@ -527,6 +611,9 @@ def main() -> int:
         return 2
     if args.preset:
         print(json.dumps(run_scenario(args)))
+        return 0
+    if args.design:
+        print(json.dumps(run_design(args)))
         return 0
     args.warmup = max(3, args.warmup)
     # a repetition's context grows from `context + warmup` to `context + warmup + steps` tokens

@@ -30,7 +30,7 @@ sigmoid_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, __nv_b
                    const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int bt_stride,
                    const int* __restrict__ cu_q, const int* __restrict__ ctx_lens, const int* __restrict__ slots,
                    const float* __restrict__ head_bias, int hq, int hkv, int gp, int block_size, int num_pages,
-                   float scale_log2, int splits, int tiles_per_split, int* __restrict__ status) {
+                   float half_scale, int splits, int tiles_per_split, int* __restrict__ status) {
   constexpr int CK = DK / 8, CV = DV / 8;
   constexpr int K_BYTES = BN * DK * 2, V_BYTES = BN * DV * 2;
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -77,7 +77,7 @@ sigmoid_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, __nv_b
     const int tl = rr / gp;
     row_ok[i] = tl < t_count;
     qpos[i] = pos_first + tl;
-    bias2[i] = (head_bias ? head_bias[h0 + rr - tl * gp] : 0.f) * 1.4426950408889634f;
+    bias2[i] = (head_bias ? head_bias[h0 + rr - tl * gp] : 0.f) * 0.5f;
   }
   float o[DV / 8][4];
 #pragma unroll
@@ -167,14 +167,17 @@ sigmoid_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, __nv_b
           mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
         }
       }
-      // ---- weights: sigmoid(x) = 1 / (1 + 2^(-x log2 e)), x = s * scale + bias; hidden keys weigh nothing
+      // ---- weights: sigmoid(x) = 0.5 + 0.5 tanh(x / 2), x = s * scale + bias (one special-function
+      // instruction per score; its error is below the bf16 rounding of the weight); hidden keys weigh nothing
       const bool need_mask = (kv0 + BN - 1 > pos_first) || (t_count < qt);
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = e >> 1;
-          float p = __fdividef(1.0f, 1.0f + fast_exp2(-fmaf(s[nt][e], scale_log2, bias2[i])));
+          float p;
+          asm("tanh.approx.f32 %0, %1;" : "=f"(p) : "f"(fmaf(s[nt][e], half_scale, bias2[i])));
+          p = fmaf(0.5f, p, 0.5f);
           if (need_mask) {
             const int key = kv0 + nt * 8 + 2 * t4 + (e & 1);
             if (!row_ok[i] || key > qpos[i]) p = 0.f;
@@ -241,7 +244,7 @@ int sigmoid_mma_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* 
   dim3 grid(((max_q_len + qt - 1) / qt) * splits, hkv * (group / gp), num_requests);
   return gllm_launch(sigmoid_mma_kernel<DK, DV>, grid, dim3(SG_THREADS), smem, stream, q, q_stride, out, out_stride,
                      partial, partial_stride, cache, block_table, bt_stride, cu_q, ctx_lens, slots, head_bias, hq, hkv,
-                     gp, block_size, num_pages, scale * 1.4426950408889634f, splits, tiles_per_split, status);
+                     gp, block_size, num_pages, 0.5f * scale, splits, tiles_per_split, status);
 }
 }  // namespace
 

@@ -18,6 +18,20 @@ __device__ __forceinline__ float siluf_(float x) { return x / (1.0f + expf(-x));
 __device__ __forceinline__ float softplusf_(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
+// Loads that stay where they are written: the look-ahead of the chunked kernels below asks for the next chunk's
+// inputs before it computes the current one, and the compiler would otherwise move the loads down to their first
+// use, behind the computation they are meant to overlap.
+__device__ __forceinline__ float load_ahead(const float* p) {
+  float v;
+  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float load_ahead(const __nv_bfloat16* p) {
+  unsigned short u;
+  asm volatile("ld.global.u16 %0, [%1];" : "=h"(u) : "l"(p));
+  return __uint_as_float(((unsigned int)u) << 16);
+}
+
 // --------------------------------------------------------------- causal convolution + SiLU
 // out[i, c] = silu(bias[c] + sum_j w[c, taps-1-j] * x[i-j, c]) over the request's own earlier tokens;
 // what lies before this step's first token comes from conv_state[slot, taps-1, channels] (the last
@@ -59,11 +73,18 @@ conv_silu_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restr
 }
 
 // --------------------------------------------------------------- selective scan
-// One group of `lanes` threads per (request, channel); each thread keeps NPT of the channel's states.
-constexpr int SCAN_NPT = 8;
+// One group of `lanes` threads per (request, channel); each thread keeps NPT of the channel's states (2 for up
+// to 64 states, so that a token costs a warp few instructions: the scan is a chain from token to token and what
+// bounds it is the length of that chain, not the amount of work; 8 beyond).
+// The tokens of a request are taken in chunks of `tc`: while one chunk is computed from shared memory,
+// the inputs of the next (step size, input and gate of every channel of the block, B and C rows) are
+// already on their way from global memory into registers, and go into the other buffer afterwards.
 constexpr int SCAN_THREADS = 128;
+constexpr int SCAN_MAX_CHUNK = 16;
+constexpr int SCAN_PF_BC = 8;      // B/C values a thread fetches ahead per chunk: tc * 2 * n_state <= 128 * 8
+constexpr int SCAN_PF_CH = 8;      // (token, channel) cells a thread fetches ahead: tc * channels per block <= 128 * 8
 
-template <typename T>
+template <typename T, int NPT>
 __global__ void __launch_bounds__(SCAN_THREADS)
 selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  convolved, activated input
                       const float* __restrict__ dt_raw,    // [n, channels]  step-size projection, before bias
@@ -76,51 +97,123 @@ selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  con
                       float* __restrict__ conv_state,      // [slots, taps-1, channels]
                       const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                       T* __restrict__ out,                 // [n, channels]  y * silu(z)
-                      int channels, int n_state, int taps, int lanes) {
+                      int channels, int n_state, int taps, int lanes, int tc) {
+  extern __shared__ float scan_smem[];
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.y;
   const int per_block = SCAN_THREADS / lanes;
-  const int c = blockIdx.x * per_block + threadIdx.x / lanes;
+  const int c0 = blockIdx.x * per_block;
+  const int cl = threadIdx.x / lanes;            // channel within the block
+  const int c = c0 + cl;
   const int sub = threadIdx.x % lanes;
   const int start = cu_q[r], end = cu_q[r + 1];
   const int slot = state_slots[r];
   const bool live = c < channels;
   const int cc = live ? c : 0;
-  float S[SCAN_NPT], a[SCAN_NPT];
+  // one buffer: B|C [tc][2 * n_state], then dt, x, silu(z) [tc][per_block] each
+  const int buf_floats = tc * (2 * n_state + 3 * per_block);
+  float S[NPT], a[NPT];
   float* sp = ssm_state + ((int64_t)slot * channels + cc) * n_state;
 #pragma unroll
-  for (int k = 0; k < SCAN_NPT; ++k) {
-    const int n = sub * SCAN_NPT + k;
+  for (int k = 0; k < NPT; ++k) {
+    const int n = sub * NPT + k;
     const bool ok = live && n < n_state;
     S[k] = ok ? sp[n] : 0.f;
-    a[k] = ok ? A[(int64_t)cc * n_state + n] : 0.f;
+    a[k] = ok ? A[(int64_t)cc * n_state + n] * 1.4426950408889634f : 0.f;    // exp(dt A) = 2^(dt A log2 e)
   }
-  const float bias = dt_bias[cc], dskip = D[cc];
-  for (int t = start; t < end; ++t) {
-    const float dt = softplusf_(dt_raw[(int64_t)t * channels + cc] + bias);
-    const float x = to_float(xc[(int64_t)t * channels + cc]);
-    const float dx = dt * x;
-    const T* brow = bc + (int64_t)t * bc_stride;
-    float y = 0.f;
+  const float dskip = D[cc];
+
+  float pf_bc[SCAN_PF_BC], pf_dt[SCAN_PF_CH], pf_x[SCAN_PF_CH], pf_z[SCAN_PF_CH];
+  auto fetch = [&](int t0, int nt) {
 #pragma unroll
-    for (int k = 0; k < SCAN_NPT; ++k) {
-      const int n = sub * SCAN_NPT + k;
-      if (n < n_state) {
-        S[k] = expf(dt * a[k]) * S[k] + dx * to_float(brow[b_off + n]);
-        y = fmaf(S[k], to_float(brow[c_off + n]), y);
+    for (int j = 0; j < SCAN_PF_BC; ++j) {
+      const int idx = threadIdx.x + j * SCAN_THREADS;
+      if (idx < nt * 2 * n_state) {
+        const int tt = idx / (2 * n_state), n = idx - tt * 2 * n_state;
+        const T* row = bc + (int64_t)(t0 + tt) * bc_stride;
+        pf_bc[j] = load_ahead(n < n_state ? row + b_off + n : row + c_off + n - n_state);
       }
     }
-    for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-    if (sub == 0 && live) {
-      const float z = to_float(xz[(int64_t)t * xz_stride + z_off + cc]);
-      out[(int64_t)t * channels + cc] = from_float<T>((y + dskip * x) * siluf_(z));
+#pragma unroll
+    for (int j = 0; j < SCAN_PF_CH; ++j) {
+      const int idx = threadIdx.x + j * SCAN_THREADS;
+      if (idx < nt * per_block) {
+        const int tt = idx / per_block, ch = c0 + idx - tt * per_block;
+        if (ch < channels) {
+          const int64_t t = t0 + tt;
+          pf_dt[j] = load_ahead(dt_raw + t * channels + ch) + dt_bias[ch];
+          pf_x[j] = load_ahead(xc + t * channels + ch);
+          pf_z[j] = load_ahead(xz + t * xz_stride + z_off + ch);
+        } else {
+          pf_dt[j] = pf_x[j] = pf_z[j] = 0.f;
+        }
+      }
     }
+  };
+  auto stash = [&](int nt, float* buf) {
+    float* bc_s = buf;
+    float* dt_s = buf + tc * 2 * n_state;
+    float* x_s = dt_s + tc * per_block;
+    float* z_s = x_s + tc * per_block;
+#pragma unroll
+    for (int j = 0; j < SCAN_PF_BC; ++j) {
+      const int idx = threadIdx.x + j * SCAN_THREADS;
+      if (idx < nt * 2 * n_state) bc_s[idx] = pf_bc[j];
+    }
+#pragma unroll
+    for (int j = 0; j < SCAN_PF_CH; ++j) {
+      const int idx = threadIdx.x + j * SCAN_THREADS;
+      if (idx < nt * per_block) {
+        dt_s[idx] = softplusf_(pf_dt[j]);
+        x_s[idx] = pf_x[j];
+        z_s[idx] = siluf_(pf_z[j]);
+      }
+    }
+  };
+
+  if (start < end) {
+    fetch(start, min(tc, end - start));
+    stash(min(tc, end - start), scan_smem);
+  }
+  __syncthreads();
+  int which = 0;
+  for (int t0 = start; t0 < end; t0 += tc, which ^= 1) {
+    const int nt = min(tc, end - t0);
+    const int next = t0 + tc;
+    const int nt_next = min(tc, end - next);
+    if (next < end) fetch(next, nt_next);
+    const float* buf = scan_smem + which * buf_floats;
+    const float* bc_s = buf;
+    const float* dt_s = buf + tc * 2 * n_state;
+    const float* x_s = dt_s + tc * per_block;
+    const float* z_s = x_s + tc * per_block;
+    T* out_p = out + (int64_t)t0 * channels + cc;
+#pragma unroll 2
+    for (int tt = 0; tt < nt; ++tt) {
+      const float dt = dt_s[tt * per_block + cl];
+      const float x = x_s[tt * per_block + cl];
+      const float dx = dt * x;
+      const float* brow = bc_s + tt * 2 * n_state;
+      float y = 0.f;
+#pragma unroll
+      for (int k = 0; k < NPT; ++k) {
+        const int n = sub * NPT + k;
+        if (n < n_state) {
+          S[k] = exp2f(dt * a[k]) * S[k] + dx * brow[n];
+          y = fmaf(S[k], brow[n_state + n], y);
+        }
+      }
+      for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+      if (sub == 0 && live) out_p[(int64_t)tt * channels] = from_float<T>((y + dskip * x) * z_s[tt * per_block + cl]);
+    }
+    if (next < end) stash(nt_next, scan_smem + (which ^ 1) * buf_floats);
+    __syncthreads();
   }
   if (live) {
 #pragma unroll
-    for (int k = 0; k < SCAN_NPT; ++k) {
-      const int n = sub * SCAN_NPT + k;
+    for (int k = 0; k < NPT; ++k) {
+      const int n = sub * NPT + k;
       if (n < n_state) sp[n] = S[k];
     }
   }
@@ -143,35 +236,317 @@ selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  con
   }
 }
 
+// --------------------------------------------------------------- the scalar gates of the exponential-gate memory
+// Per (request, head): i = cap * tanh((i_raw + i_bias) / cap), f = logsigmoid(cap * tanh((f_raw + f_bias) / cap)) for
+// every token of the step (in parallel), then the running maximum m' = max(f + m, i) token after token (one thread
+// per head: two operations a token).  work [n, 4 * heads] = i | f | m before the token | m after it; the
+// request's maximum in mstate is brought up to date here and nowhere else, so the blocks of the recurrence
+// kernel, which may run at different times, all see the same values.
+__global__ void __launch_bounds__(128)
+exp_gate_scan_kernel(const float* __restrict__ gates, int64_t gates_stride, const float* __restrict__ gate_bias, float cap,
+                     float* __restrict__ mstate, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
+                     float* __restrict__ work, int heads) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int start = cu_q[r], end = cu_q[r + 1];
+  const int slot = state_slots[r];
+  const int64_t total = (int64_t)(end - start) * heads;
+  for (int64_t idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const int64_t t = start + idx / heads;
+    const int h = (int)(idx % heads);
+    const float* g = gates + t * gates_stride;
+    work[t * 4 * heads + h] = cap * tanhf((g[h] + gate_bias[h]) / cap);
+    work[t * 4 * heads + heads + h] = logsigmoidf_(cap * tanhf((g[heads + h] + gate_bias[heads + h]) / cap));
+  }
+  __syncthreads();
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    float m = mstate[(int64_t)slot * heads + h];
+    for (int64_t t0 = start; t0 < end; t0 += 8) {      // eight tokens' gates are asked for at once, then chained
+      float ig[8], fg[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool ok = t0 + u < end;
+        const float* w = work + (t0 + (ok ? u : 0)) * 4 * heads;
+        ig[u] = __ldcg(w + h);
+        fg[u] = __ldcg(w + heads + h);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (t0 + u < end) {
+          float* w = work + (t0 + u) * 4 * heads;
+          w[2 * heads + h] = m;
+          m = fmaxf(fg[u] + m, ig[u]);
+          w[3 * heads + h] = m;
+        }
+      }
+    }
+    mstate[(int64_t)slot * heads + h] = m;
+  }
+}
+
 // --------------------------------------------------------------- matrix recurrence per head
-// S [dk, dvx] per (request, head).  mode 0 (gated linear attention): a[d] = f[d], b[d] = 1 - f[d] with
+// S [dvx, dk] per (request, head), stored column by column: S[c, d] is what key channel d holds of value
+// column c.  mode 0 (gated linear attention): a[d] = f[d], b[d] = 1 - f[d] with
 // f = lower + (1 - lower) * sigmoid(f_raw + f_bias) and q = silu(q_raw).  mode 1 (matrix memory with
 // exponential gates): i = cap * tanh((i_raw + i_bias) / cap), f = logsigmoid(cap * tanh((f_raw + f_bias) / cap)),
 // m' = max(f + m, i), a = exp(f + m - m'), b[d] = exp(i - m') * k[d], q = q_raw * q_scale; the state
 // has one column more than there are value columns, fed with ones, which carries the normaliser n, and
 // the output gets two columns more: n . q and exp(-m').
-// A block owns COLS columns of one (request, head); `lanes` threads share a column, each keeping DPT rows.
-constexpr int REC_DPT = 16;
+// A block owns `cols` columns of one (request, head); `lanes` threads share a column, each keeping DPT of its
+// key channels (4 for up to 128 key channels, 16 beyond: the recurrence is a chain from token to token, bounded
+// by the instructions a warp spends per token, so the state is spread over many threads).  Tokens are taken in chunks of `tc`: while a chunk is computed from shared memory, the raw
+// inputs of the next one are on their way into registers; they are turned into the effective q, gate (or
+// key) and v and put into the other buffer afterwards.
 constexpr int REC_THREADS = 256;
-constexpr int REC_CHUNK = 8;
+constexpr int REC_MAX_CHUNK = 16;
+constexpr int REC_PF = 8;          // look-ahead registers per operand: tc * lanes * DPT <= 256 * 8, tc * cols <= 256 * 8
 
-template <typename T>
+template <typename T, int DPT>
 __global__ void __launch_bounds__(REC_THREADS)
 matrix_recurrence_kernel(int mode,
                          const T* __restrict__ q, int64_t q_stride,       // [n, heads * dk] at its offset
                          const T* __restrict__ k, int64_t k_stride,       // mode 1
                          const T* __restrict__ v, int64_t v_stride,       // [n, heads * dv]
                          const float* __restrict__ gates, int64_t gates_stride,
-                         // mode 0: f_raw [n, heads * dk]; mode 1: [n, 2 * heads]: i_raw | f_raw
-                         const float* __restrict__ gate_bias,             // same layout as one row of gates
+                         // mode 0: f_raw [n, heads * dk]; mode 1: the gate scan's work [n, 4 * heads]
+                         const float* __restrict__ gate_bias,             // mode 0: [heads * dk]
                          const float* __restrict__ lower,                 // mode 0: [heads * dk]
-                         float cap, float q_scale,
-                         float* __restrict__ state,                       // [slots, heads, dk, dvx]
-                         float* __restrict__ mstate,                      // mode 1: [slots, heads]
+                         float q_scale,
+                         float* __restrict__ state,                       // [slots, heads, dvx, dk]
                          const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                          float* __restrict__ out, int64_t out_stride,     // [n, heads * out_cols]
-                         int heads, int dk, int dv, int lanes) {
-  extern __shared__ float smem[];
+                         int heads, int dk, int dv, int lanes, int tc) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int cols = REC_THREADS / lanes;
+  const int dkp = lanes * DPT;                 // padded row of the staged operands
+  const int dvx = dv + (mode == 1 ? 1 : 0);
+  const int out_cols = dv + (mode == 1 ? 2 : 0);
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int cix = threadIdx.x / lanes;
+  const int col = blockIdx.x * cols + cix;
+  const int sub = threadIdx.x % lanes;
+  const int start = cu_q[r], end = cu_q[r + 1];
+  const int slot = state_slots[r];
+  const bool live = col < dvx;
+  // one buffer: q [tc][dkp], gate or key [tc][dkp], v [tc][cols], keep | take | exp(-m') [3][tc] (padded to 4)
+  const int buf_floats = tc * (2 * dkp + cols + 4);
+  float* const bufs = smem;
+
+  float S[DPT];
+  float* sp = state + (((int64_t)slot * heads + h) * dvx + (live ? col : 0)) * dk;
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const int d = sub * DPT + i;
+    S[i] = (live && d < dk) ? sp[d] : 0.f;
+  }
+
+  float pq[REC_PF], pg[REC_PF], pv[REC_PF], pi = 0.f, pf = 0.f, pmp = 0.f, pmn = 0.f;
+  auto fetch = [&](int t0, int nt) {
+#pragma unroll
+    for (int j = 0; j < REC_PF; ++j) {
+      const int idx = threadIdx.x + j * REC_THREADS;
+      if (idx < nt * dkp) {
+        const int tt = idx / dkp, d = idx - tt * dkp;
+        pq[j] = pg[j] = 0.f;
+        if (d < dk) {
+          const int64_t t = t0 + tt;
+          const int hd = h * dk + d;
+          pq[j] = load_ahead(q + t * q_stride + hd);
+          pg[j] = mode == 1 ? load_ahead(k + t * k_stride + hd) : load_ahead(gates + t * gates_stride + hd) + gate_bias[hd];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < REC_PF; ++j) {
+      const int idx = threadIdx.x + j * REC_THREADS;
+      if (idx < nt * cols) {
+        const int tt = idx / cols, cg = blockIdx.x * cols + idx - tt * cols;
+        pv[j] = cg < dv ? load_ahead(v + (int64_t)(t0 + tt) * v_stride + (int64_t)h * dv + cg) : 1.0f;
+      }
+    }
+    if (mode == 1 && (int)threadIdx.x < nt) {
+      const float* g = gates + (int64_t)(t0 + threadIdx.x) * gates_stride;
+      pi = load_ahead(g + h);
+      pf = load_ahead(g + heads + h);
+      pmp = load_ahead(g + 2 * heads + h);
+      pmn = load_ahead(g + 3 * heads + h);
+    }
+  };
+  auto stash = [&](int nt, float* buf) {
+    float* q_s = buf;
+    float* g_s = buf + tc * dkp;
+    float* v_s = g_s + tc * dkp;
+    float* sc_s = v_s + tc * cols;
+#pragma unroll
+    for (int j = 0; j < REC_PF; ++j) {
+      const int idx = threadIdx.x + j * REC_THREADS;
+      if (idx < nt * dkp) {
+        const int d = idx % dkp;
+        if (mode == 1) {
+          q_s[idx] = pq[j] * q_scale;
+          g_s[idx] = pg[j];
+        } else {
+          const float lo = d < dk ? lower[h * dk + d] : 0.f;
+          q_s[idx] = d < dk ? siluf_(pq[j]) : 0.f;
+          g_s[idx] = d < dk ? lo + (1.0f - lo) * sigmoidf_(pg[j]) : 0.f;
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < REC_PF; ++j) {
+      const int idx = threadIdx.x + j * REC_THREADS;
+      if (idx < nt * cols) v_s[idx] = pv[j];
+    }
+    if (mode == 1 && (int)threadIdx.x < nt) {
+      sc_s[threadIdx.x] = expf(pf + pmp - pmn);          // keep
+      sc_s[tc + threadIdx.x] = expf(pi - pmn);           // take
+      sc_s[2 * tc + threadIdx.x] = expf(-pmn);
+    }
+  };
+
+  if (start < end) {
+    fetch(start, min(tc, end - start));
+    stash(min(tc, end - start), bufs);
+  }
+  __syncthreads();
+  int which = 0;
+  for (int t0 = start; t0 < end; t0 += tc, which ^= 1) {
+    const int nt = min(tc, end - t0);
+    const int next = t0 + tc;
+    const int nt_next = min(tc, end - next);
+    if (next < end) fetch(next, nt_next);
+    const float* buf = bufs + which * buf_floats;
+    const float* q_s = buf + sub * DPT;
+    const float* g_s = buf + tc * dkp + sub * DPT;
+    const float* v_s = buf + 2 * tc * dkp;
+    const float* sc_s = v_s + tc * cols;
+    float* out_p = out + (int64_t)t0 * out_stride + (int64_t)h * out_cols;
+#pragma unroll 2
+    for (int tt = 0; tt < nt; ++tt) {
+      const float vj = v_s[tt * cols + cix];
+      float keep = 0.f, take = 0.f;
+      if (mode == 1) {
+        keep = sc_s[tt];
+        take = sc_s[tc + tt];
+      }
+      float o = 0.f;
+      const float4* q4 = reinterpret_cast<const float4*>(q_s + tt * dkp);
+      const float4* g4 = reinterpret_cast<const float4*>(g_s + tt * dkp);
+#pragma unroll
+      for (int i4 = 0; i4 < DPT / 4; ++i4) {
+        const float4 qq = q4[i4], gg = g4[i4];
+        const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ga[4] = {gg.x, gg.y, gg.z, gg.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = i4 * 4 + e;
+          const float a = mode == 1 ? keep : ga[e];
+          const float b = mode == 1 ? take * ga[e] : 1.0f - ga[e];
+          S[i] = a * S[i] + b * vj;
+          o = fmaf(S[i], qa[e], o);
+        }
+      }
+      for (int off = lanes >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (sub == 0 && live) out_p[(int64_t)tt * out_stride + col] = o;
+      if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) out_p[(int64_t)tt * out_stride + dv + 1] = sc_s[2 * tc + tt];
+    }
+    if (next < end) stash(nt_next, bufs + (which ^ 1) * buf_floats);
+    __syncthreads();
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const int d = sub * DPT + i;
+      if (d < dk) sp[d] = S[i];
+    }
+  }
+}
+
+// --------------------------------------------------------------- one token per request
+// Steps in which every request brings a single token (decoding) have no chain to follow: each state element is
+// read, updated and written once, so these kernels are laid out for the memory system instead.  A thread owns
+// four neighbouring elements of a state row (one 16-byte access each way when the row length allows), takes its
+// operands straight from global memory, and the threads that share a row add their parts by shuffles.
+template <typename T>
+__global__ void __launch_bounds__(128)
+selective_scan_step_kernel(const T* __restrict__ xc, const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
+                           const float* __restrict__ A, const T* __restrict__ bc, int64_t bc_stride, int b_off,
+                           int c_off, const float* __restrict__ D, const T* __restrict__ xz, int64_t xz_stride,
+                           int z_off, float* __restrict__ ssm_state, float* __restrict__ conv_state,
+                           const int* __restrict__ cu_q, const int* __restrict__ state_slots, T* __restrict__ out,
+                           int channels, int n_state, int taps, int lanes) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.y;
+  const int per_block = 128 / lanes;
+  const int c = blockIdx.x * per_block + threadIdx.x / lanes;
+  const int sub = threadIdx.x % lanes;
+  const int t = cu_q[r];
+  if (cu_q[r + 1] - t != 1) return;                       // (the host picks this kernel for single tokens only)
+  const int slot = state_slots[r];
+  const bool live = c < channels;
+  const int cc = live ? c : 0;
+  const float dt = softplusf_(dt_raw[(int64_t)t * channels + cc] + dt_bias[cc]);
+  const float x = to_float(xc[(int64_t)t * channels + cc]);
+  const float dx = dt * x;
+  const T* brow = bc + (int64_t)t * bc_stride;
+  float* sp = ssm_state + ((int64_t)slot * channels + cc) * n_state;
+  const bool vec = (n_state & 3) == 0;
+  float y = 0.f;
+  for (int n0 = sub * 4; n0 < n_state; n0 += lanes * 4) {
+    float S[4], a[4];
+    if (vec) {
+      const float4 s4 = *reinterpret_cast<const float4*>(sp + n0);
+      const float4 a4 = *reinterpret_cast<const float4*>(A + (int64_t)cc * n_state + n0);
+      S[0] = s4.x; S[1] = s4.y; S[2] = s4.z; S[3] = s4.w;
+      a[0] = a4.x; a[1] = a4.y; a[2] = a4.z; a[3] = a4.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const bool ok = n0 + e < n_state;
+        S[e] = ok ? sp[n0 + e] : 0.f;
+        a[e] = ok ? A[(int64_t)cc * n_state + n0 + e] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if (n0 + e < n_state) {
+        S[e] = exp2f(dt * (a[e] * 1.4426950408889634f)) * S[e] + dx * to_float(brow[b_off + n0 + e]);
+        y = fmaf(S[e], to_float(brow[c_off + n0 + e]), y);
+      }
+    }
+    if (live) {
+      if (vec) {
+        *reinterpret_cast<float4*>(sp + n0) = make_float4(S[0], S[1], S[2], S[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (n0 + e < n_state) sp[n0 + e] = S[e];
+      }
+    }
+  }
+  for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+  if (sub == 0 && live) {
+    const float z = to_float(xz[(int64_t)t * xz_stride + z_off + cc]);
+    out[(int64_t)t * channels + cc] = from_float<T>((y + D[cc] * x) * siluf_(z));
+    const int keep = taps - 1;                           // the convolution's memory moves on by one input
+    float* cs = conv_state + (int64_t)slot * keep * channels + cc;
+    for (int k = 0; k + 1 < keep; ++k) cs[(int64_t)k * channels] = cs[(int64_t)(k + 1) * channels];
+    if (keep > 0) cs[(int64_t)(keep - 1) * channels] = to_float(xz[(int64_t)t * xz_stride + cc]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(REC_THREADS)
+matrix_recurrence_step_kernel(int mode, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ k,
+                              int64_t k_stride, const T* __restrict__ v, int64_t v_stride,
+                              const float* __restrict__ gates, int64_t gates_stride, const float* __restrict__ gate_bias,
+                              const float* __restrict__ lower, float q_scale, float* __restrict__ state,
+                              const int* __restrict__ cu_q,
+                              const int* __restrict__ state_slots, float* __restrict__ out, int64_t out_stride, int heads,
+                              int dk, int dv, int lanes) {
   pdl_trigger();
   pdl_wait();
   const int cols = REC_THREADS / lanes;
@@ -180,100 +555,64 @@ matrix_recurrence_kernel(int mode,
   const int r = blockIdx.z, h = blockIdx.y;
   const int col = blockIdx.x * cols + threadIdx.x / lanes;
   const int sub = threadIdx.x % lanes;
-  const int start = cu_q[r], end = cu_q[r + 1];
+  const int64_t t = cu_q[r];
+  if (cu_q[r + 1] - t != 1) return;
   const int slot = state_slots[r];
   const bool live = col < dvx;
-  float* q_s = smem;                              // [CHUNK, dk]
-  float* a_s = q_s + REC_CHUNK * dk;              // [CHUNK, dk]  (mode 0)
-  float* b_s = a_s + REC_CHUNK * dk;              // [CHUNK, dk]
-  float* v_s = b_s + REC_CHUNK * dk;              // [CHUNK, cols]
-  float* keep_s = v_s + REC_CHUNK * cols;         // [CHUNK]  mode 1: exp(f + m - m')
-  float* take_s = keep_s + REC_CHUNK;             // [CHUNK]  mode 1: exp(i - m')
-  float* e_s = take_s + REC_CHUNK;                // [CHUNK]  mode 1: exp(-m')
-  __shared__ float m_run;
-
-  float S[REC_DPT];
-  float* sp = state + (((int64_t)slot * heads + h) * dk) * dvx + (live ? col : 0);
-#pragma unroll
-  for (int i = 0; i < REC_DPT; ++i) {
-    const int d = sub * REC_DPT + i;
-    S[i] = (live && d < dk) ? sp[(int64_t)d * dvx] : 0.f;
+  float keep = 0.f, take = 0.f, m_new = 0.f;
+  if (mode == 1) {
+    const float* g = gates + t * gates_stride;            // the gate scan's work: i | f | m before | m after
+    m_new = g[3 * heads + h];
+    keep = expf(g[heads + h] + g[2 * heads + h] - m_new);
+    take = expf(g[h] - m_new);
   }
-  if (threadIdx.x == 0) m_run = mode == 1 ? mstate[(int64_t)slot * heads + h] : 0.f;
-  __syncthreads();
-
-  for (int t0 = start; t0 < end; t0 += REC_CHUNK) {
-    const int nt = min(REC_CHUNK, end - t0);
-    // ---- stage the chunk: effective q, a, b per (token, row), v per (token, column)
-    if (mode == 1) {
-      if (threadIdx.x == 0) {          // the scalar gates run in sequence: the maximum is carried
-        float m = m_run;
-        for (int tt = 0; tt < nt; ++tt) {
-          const float* g = gates + (int64_t)(t0 + tt) * gates_stride;
-          const float ig = cap * tanhf((g[h] + gate_bias[h]) / cap);
-          const float fg = logsigmoidf_(cap * tanhf((g[heads + h] + gate_bias[heads + h]) / cap));
-          const float m_new = fmaxf(fg + m, ig);
-          keep_s[tt] = expf(fg + m - m_new);
-          take_s[tt] = expf(ig - m_new);
-          e_s[tt] = expf(-m_new);
-          m = m_new;
-        }
-        m_run = m;
-      }
-      __syncthreads();
-      for (int idx = threadIdx.x; idx < nt * dk; idx += REC_THREADS) {
-        const int tt = idx / dk, d = idx - tt * dk;
-        const int64_t t = t0 + tt;
-        q_s[idx] = to_float(q[t * q_stride + (int64_t)h * dk + d]) * q_scale;
-        b_s[idx] = take_s[tt] * to_float(k[t * k_stride + (int64_t)h * dk + d]);
-      }
+  const float vj = !live ? 0.f : (col < dv ? to_float(v[t * v_stride + (int64_t)h * dv + col]) : 1.0f);
+  float* sp = state + (((int64_t)slot * heads + h) * dvx + (live ? col : 0)) * dk;
+  const bool vec = (dk & 3) == 0;
+  float o = 0.f;
+  for (int d0 = sub * 4; d0 < dk; d0 += lanes * 4) {
+    float S[4];
+    if (vec) {
+      const float4 s4 = *reinterpret_cast<const float4*>(sp + d0);
+      S[0] = s4.x; S[1] = s4.y; S[2] = s4.z; S[3] = s4.w;
     } else {
-      for (int idx = threadIdx.x; idx < nt * dk; idx += REC_THREADS) {
-        const int tt = idx / dk, d = idx - tt * dk;
-        const int64_t t = t0 + tt;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) S[e] = d0 + e < dk ? sp[d0 + e] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int d = d0 + e;
+      if (d < dk) {
         const int hd = h * dk + d;
-        const float lo = lower[hd];
-        const float f = lo + (1.0f - lo) * sigmoidf_(gates[t * gates_stride + hd] + gate_bias[hd]);
-        a_s[idx] = f;
-        b_s[idx] = 1.0f - f;
-        q_s[idx] = siluf_(to_float(q[t * q_stride + hd]));
-      }
-    }
-    for (int idx = threadIdx.x; idx < nt * cols; idx += REC_THREADS) {
-      const int tt = idx / cols, cix = idx - tt * cols;
-      const int cg = blockIdx.x * cols + cix;
-      v_s[idx] = cg < dv ? to_float(v[(int64_t)(t0 + tt) * v_stride + (int64_t)h * dv + cg]) : 1.0f;
-    }
-    __syncthreads();
-    // ---- the recurrence over the chunk's tokens
-    for (int tt = 0; tt < nt; ++tt) {
-      const float vj = v_s[tt * cols + threadIdx.x / lanes];
-      const float keep = mode == 1 ? keep_s[tt] : 0.f;
-      float o = 0.f;
-#pragma unroll
-      for (int i = 0; i < REC_DPT; ++i) {
-        const int d = sub * REC_DPT + i;
-        if (d < dk) {
-          const float a = mode == 1 ? keep : a_s[tt * dk + d];
-          S[i] = a * S[i] + b_s[tt * dk + d] * vj;
-          o = fmaf(S[i], q_s[tt * dk + d], o);
+        float a, b, qe;
+        if (mode == 1) {
+          a = keep;
+          b = take * to_float(k[t * k_stride + hd]);
+          qe = to_float(q[t * q_stride + hd]) * q_scale;
+        } else {
+          const float lo = lower[hd];
+          a = lo + (1.0f - lo) * sigmoidf_(gates[t * gates_stride + hd] + gate_bias[hd]);
+          b = 1.0f - a;
+          qe = siluf_(to_float(q[t * q_stride + hd]));
         }
+        S[e] = a * S[e] + b * vj;
+        o = fmaf(S[e], qe, o);
       }
-      for (int off = lanes >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (sub == 0 && live) out[(int64_t)(t0 + tt) * out_stride + (int64_t)h * out_cols + col] = o;
-      if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0)
-        out[(int64_t)(t0 + tt) * out_stride + (int64_t)h * out_cols + dv + 1] = e_s[tt];
     }
-    __syncthreads();
-  }
-  if (live) {
+    if (live) {
+      if (vec) {
+        *reinterpret_cast<float4*>(sp + d0) = make_float4(S[0], S[1], S[2], S[3]);
+      } else {
 #pragma unroll
-    for (int i = 0; i < REC_DPT; ++i) {
-      const int d = sub * REC_DPT + i;
-      if (d < dk) sp[(int64_t)d * dvx] = S[i];
+        for (int e = 0; e < 4; ++e)
+          if (d0 + e < dk) sp[d0 + e] = S[e];
+      }
     }
   }
-  if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) mstate[(int64_t)slot * heads + h] = m_run;
+  for (int off = lanes >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+  float* orow = out + t * out_stride + (int64_t)h * out_cols;
+  if (sub == 0 && live) orow[col] = o;
+  if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) orow[dv + 1] = expf(-m_new);
 }
 
 // --------------------------------------------------------------- per-head output norm
@@ -328,32 +667,74 @@ template <typename T>
 int selective_scan_launch(const T* xc, const float* dt_raw, const float* dt_bias, const float* A, const T* bc,
                           int64_t bc_stride, int b_off, int c_off, const float* D, const T* xz, int64_t xz_stride,
                           int z_off, float* ssm_state, float* conv_state, const int* cu_q, const int* state_slots,
-                          T* out, int num_requests, int channels, int n_state, int taps, cudaStream_t stream) {
+                          T* out, int num_requests, int max_q_len, int channels, int n_state, int taps,
+                          cudaStream_t stream) {
   if (num_requests <= 0) return 0;
-  const int lanes = pow2_at_least((n_state + SCAN_NPT - 1) / SCAN_NPT);
+  if (max_q_len == 1 && taps >= 1 && taps <= MAX_TAPS && num_requests <= 65535) {
+    int lanes = pow2_at_least((n_state + 3) / 4);
+    if (lanes > 32) lanes = 32;
+    const int per_block = 128 / lanes;
+    return gllm_launch(selective_scan_step_kernel<T>, dim3((channels + per_block - 1) / per_block, num_requests),
+                       dim3(128), 0, stream, xc, dt_raw, dt_bias, A, bc, bc_stride, b_off, c_off, D, xz, xz_stride, z_off,
+                       ssm_state, conv_state, cu_q, state_slots, out, channels, n_state, taps, lanes);
+  }
+  const int npt = n_state <= 64 ? 2 : 8;
+  const int lanes = pow2_at_least((n_state + npt - 1) / npt);
   if (lanes > 32 || taps < 1 || taps > MAX_TAPS || num_requests > 65535) return (int)cudaErrorInvalidValue;
   const int per_block = SCAN_THREADS / lanes;
-  return gllm_launch(selective_scan_kernel<T>, dim3((channels + per_block - 1) / per_block, num_requests),
-                     dim3(SCAN_THREADS), 0, stream, xc, dt_raw, dt_bias, A, bc, bc_stride, b_off, c_off, D, xz, xz_stride,
-                     z_off, ssm_state, conv_state, cu_q, state_slots, out, channels, n_state, taps, lanes);
+  // tokens per chunk: as many as a thread's look-ahead registers hold of the chunk's B and C values
+  int tc = SCAN_MAX_CHUNK;
+  while (tc > 1 && (tc * 2 * n_state > SCAN_THREADS * SCAN_PF_BC || tc * per_block > SCAN_THREADS * SCAN_PF_CH)) tc >>= 1;
+  if (tc * 2 * n_state > SCAN_THREADS * SCAN_PF_BC || tc * per_block > SCAN_THREADS * SCAN_PF_CH)
+    return (int)cudaErrorInvalidValue;
+  const size_t smem = 2 * sizeof(float) * (size_t)tc * (2 * n_state + 3 * per_block);
+  auto kernel = npt == 2 ? selective_scan_kernel<T, 2> : selective_scan_kernel<T, 8>;
+  return gllm_launch(kernel, dim3((channels + per_block - 1) / per_block, num_requests),
+                     dim3(SCAN_THREADS), smem, stream, xc, dt_raw, dt_bias, A, bc, bc_stride, b_off, c_off, D, xz,
+                     xz_stride, z_off, ssm_state, conv_state, cu_q, state_slots, out, channels, n_state, taps, lanes, tc);
 }
 
 template <typename T>
 int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k, int64_t k_stride, const T* v,
                              int64_t v_stride, const float* gates, int64_t gates_stride, const float* gate_bias,
-                             const float* lower, float cap, float q_scale, float* state, float* mstate,
+                             const float* lower, float cap, float q_scale, float* state, float* mstate, float* work,
                              const int* cu_q, const int* state_slots, float* out, int64_t out_stride,
-                             int num_requests, int heads, int dk, int dv, cudaStream_t stream) {
+                             int num_requests, int max_q_len, int heads, int dk, int dv, cudaStream_t stream) {
   if (num_requests <= 0) return 0;
-  const int lanes = pow2_at_least((dk + REC_DPT - 1) / REC_DPT);
-  if (lanes > 32 || heads > 65535 || num_requests > 65535 || dk < 1 || dv < 1) return (int)cudaErrorInvalidValue;
-  const int cols = REC_THREADS / lanes;
+  if (heads > 65535 || num_requests > 65535 || dk < 1 || dv < 1 || dk > 512) return (int)cudaErrorInvalidValue;
   const int dvx = dv + (mode == 1 ? 1 : 0);
-  const size_t smem = sizeof(float) * ((size_t)3 * REC_CHUNK * dk + (size_t)REC_CHUNK * cols + 3 * REC_CHUNK);
-  if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-  return gllm_launch(matrix_recurrence_kernel<T>, dim3((dvx + cols - 1) / cols, heads, num_requests), dim3(REC_THREADS),
-                     smem, stream, mode, q, q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias, lower, cap,
-                     q_scale, state, mstate, cu_q, state_slots, out, out_stride, heads, dk, dv, lanes);
+  if (mode == 1) {
+    if (work == nullptr || mstate == nullptr) return (int)cudaErrorInvalidValue;
+    const int rc = gllm_launch(exp_gate_scan_kernel, dim3(num_requests), dim3(128), 0, stream, gates, gates_stride,
+                               gate_bias, cap, mstate, cu_q, state_slots, work, heads);
+    if (rc != 0) return rc;
+    gates = work;
+    gates_stride = 4 * (int64_t)heads;
+  }
+  if (max_q_len == 1) {
+    int lanes = pow2_at_least((dk + 3) / 4);
+    if (lanes > 32) lanes = 32;
+    const int cols = REC_THREADS / lanes;
+    return gllm_launch(matrix_recurrence_step_kernel<T>, dim3((dvx + cols - 1) / cols, heads, num_requests),
+                       dim3(REC_THREADS), 0, stream, mode, q, q_stride, k, k_stride, v, v_stride, gates, gates_stride,
+                       gate_bias, lower, q_scale, state, cu_q, state_slots, out, out_stride, heads, dk, dv, lanes);
+  }
+  const int dpt = dk <= 128 ? 4 : 16;
+  int lanes = pow2_at_least((dk + dpt - 1) / dpt);
+  if (lanes < 2) lanes = 2;                      // at most 128 columns per block
+  const int cols = REC_THREADS / lanes;
+  const int dkp = lanes * dpt;
+  int tc = REC_MAX_CHUNK;
+  while (tc > 1 && (tc * dkp > REC_THREADS * REC_PF || tc * cols > REC_THREADS * REC_PF)) tc >>= 1;
+  const size_t smem = sizeof(float) * 2 * (size_t)tc * (2 * dkp + cols + 4);
+  auto kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4> : matrix_recurrence_kernel<T, 16>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return gllm_launch(kernel, dim3((dvx + cols - 1) / cols, heads, num_requests), dim3(REC_THREADS), smem, stream, mode,
+                     q, q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias, lower, q_scale, state, cu_q,
+                     state_slots, out, out_stride, heads, dk, dv, lanes, tc);
 }
 
 template <typename T>
@@ -379,20 +760,20 @@ int head_norm_launch(const float* o, int64_t o_stride, int o_cols, int with_den,
                                        const T* bc, int64_t bc_stride, int b_off, int c_off, const float* D,          \
                                        const T* xz, int64_t xz_stride, int z_off, float* ssm_state, float* conv_state, \
                                        const int* cu_q, const int* state_slots, T* out, int num_requests,             \
-                                       int channels, int n_state, int taps, cudaStream_t stream) {                    \
+                                       int max_q_len, int channels, int n_state, int taps, cudaStream_t stream) {     \
     return selective_scan_launch<T>(xc, dt_raw, dt_bias, A, bc, bc_stride, b_off, c_off, D, xz, xz_stride, z_off,     \
-                                    ssm_state, conv_state, cu_q, state_slots, out, num_requests, channels, n_state,   \
-                                    taps, stream);                                                                    \
+                                    ssm_state, conv_state, cu_q, state_slots, out, num_requests, max_q_len, channels, \
+                                    n_state, taps, stream);                                                           \
   }                                                                                                                   \
   GLLM_API int gllm_matrix_recurrence_##S(int mode, const T* q, int64_t q_stride, const T* k, int64_t k_stride,       \
                                           const T* v, int64_t v_stride, const float* gates, int64_t gates_stride,     \
                                           const float* gate_bias, const float* lower, float cap, float q_scale,       \
-                                          float* state, float* mstate, const int* cu_q, const int* state_slots,       \
-                                          float* out, int64_t out_stride, int num_requests, int heads, int dk,        \
-                                          int dv, cudaStream_t stream) {                                              \
+                                          float* state, float* mstate, float* work, const int* cu_q,                  \
+                                          const int* state_slots, float* out, int64_t out_stride, int num_requests,   \
+                                          int max_q_len, int heads, int dk, int dv, cudaStream_t stream) {            \
     return matrix_recurrence_launch<T>(mode, q, q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias,   \
-                                       lower, cap, q_scale, state, mstate, cu_q, state_slots, out, out_stride,        \
-                                       num_requests, heads, dk, dv, stream);                                          \
+                                       lower, cap, q_scale, state, mstate, work, cu_q, state_slots, out, out_stride,  \
+                                       num_requests, max_q_len, heads, dk, dv, stream);                               \
   }                                                                                                                   \
   GLLM_API int gllm_head_norm_##S(const float* o, int64_t o_stride, int o_cols, int with_den, float den_eps,          \
                                   const float* w, int w_head_stride, const T* gate, int64_t gate_stride, T* out,      \

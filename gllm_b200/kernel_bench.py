@@ -220,6 +220,140 @@ def argmax(rows=8, vocab=128256, iters=5, peaks=None):
             "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "shape": dict(rows=rows, vocab=vocab)}
 
 
+# ------------------------------------------------------------------ kernels of the mixers with a state
+class _Scratch:
+    def __init__(self):
+        self.b = {}
+
+    def get(self, name, n, dt):
+        if name not in self.b or self.b[name].numel() < n:
+            self.b[name] = torch.empty(n, dtype=dt, device="cuda")
+        return self.b[name][:n]
+
+
+class _Batch:
+    """What the kernels read of a step: ``requests`` requests of ``q_len`` tokens after ``context`` cached ones."""
+
+    def __init__(self, requests, q_len, context):
+        self.num_requests, self.max_q_len, self.max_seq_len = requests, q_len, context + q_len
+        self.cu_q = (torch.arange(requests + 1, dtype=torch.int32, device="cuda") * q_len).contiguous()
+        self.context_lens = torch.full((requests,), context, dtype=torch.int32, device="cuda")
+        self.state_slots = torch.arange(requests, dtype=torch.int32, device="cuda")
+        self.positions = (context + torch.arange(q_len, dtype=torch.int32, device="cuda")).repeat(requests).contiguous()
+        self.token_row = torch.arange(requests, dtype=torch.int32, device="cuda").repeat_interleave(q_len).contiguous()
+        self.workspace = _Scratch()
+
+
+def _result(name, us, peaks, shape, nbytes=None, flops=None):
+    out = {"kernel": name, "us": round(us, 2), "shape": shape}
+    if nbytes is not None:
+        gbs = nbytes / us / 1e3
+        out.update(bytes=int(nbytes), achieved_gbs=round(gbs, 1), frac_of_hbm_peak=round(gbs / peaks["hbm_gbs"], 4))
+    if flops is not None:
+        tf = flops / us / 1e6
+        out.update(flops=flops, achieved_tflops=round(tf, 2), frac_of_bf16_peak=round(tf / peaks["bf16_tflops"], 4))
+    return out
+
+
+def sigmoid_attention(tokens=2048, batch=1, context=0, hq=32, hkv=8, dk=64, dv=64, block_size=16, iters=5, peaks=None,
+                      mma=1):
+    """``batch`` requests of ``tokens`` new tokens over ``context`` cached ones (tokens=1: a decode step)."""
+    from gllm_b200.ops import stateful
+
+    stateful.USE_TENSOR_CORES = bool(mma)
+    pages_per_req = -(-(context + tokens) // block_size)
+    num_pages = batch * pages_per_req + 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    pool = torch.randn((num_pages, block_size * hkv * (dk + dv)), generator=g, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(num_pages - 1, generator=g, device="cuda").to(torch.int32).view(batch, pages_per_req).contiguous()
+    qkv = torch.randn(batch * tokens, hq * dk + hkv * (dk + dv), device="cuda").to(torch.bfloat16)
+    bias = torch.full((hq,), -4.0, device="cuda")
+    b = _Batch(batch, tokens, context)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: stateful.sigmoid_attention(qkv, pool, table, b.positions, b.token_row, bias, hq, hkv, dk, dv, block_size,
+                                            dk ** -0.5, batch=b)
+    us = _time(fn, iters, flush)
+    flops = 2.0 * (dk + dv) * hq * batch * (tokens * context + tokens * (tokens + 1) / 2)
+    nbytes = batch * (context + tokens) * hkv * (dk + dv) * 2 + qkv.numel() * 2
+    return _result("sigmoid_attention (mma.sync)" if mma else "sigmoid_attention (CUDA cores)", us, peaks,
+                   dict(tokens=tokens, batch=batch, context=context, heads=hq, kv_heads=hkv, dk=dk, dv=dv), nbytes, flops)
+
+
+def matrix_recurrence(tokens=2048, batch=1, heads=16, dk=64, dv=128, mode=0, iters=5, peaks=None):
+    """mode 0: gated linear attention; mode 1: the matrix memory with exponential gates."""
+    from gllm_b200.ops import stateful
+
+    n = batch * tokens
+    q = torch.randn(n, heads * dk, device="cuda").to(torch.bfloat16)
+    k = torch.randn(n, heads * dk, device="cuda").to(torch.bfloat16)
+    v = torch.randn(n, heads * dv, device="cuda").to(torch.bfloat16)
+    gates = torch.randn(n, heads * dk if mode == 0 else 2 * heads, device="cuda")
+    gbias = torch.zeros(gates.shape[1], device="cuda")
+    lower = torch.rand(heads * dk, device="cuda") * 0.9
+    state = torch.zeros(batch + 1, heads, dv + mode, dk, device="cuda")
+    mstate = torch.zeros(batch + 1, heads, device="cuda")
+    b = _Batch(batch, tokens, 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: stateful.matrix_recurrence(mode, q, k if mode else None, v, gates, gbias, None if mode else lower, 15.0,
+                                            dk ** -0.5, state, mstate if mode else None, b.cu_q, b.state_slots, batch,
+                                            heads, dk, dv, max_q_len=tokens)
+    us = _time(fn, iters, flush)
+    nbytes = 2 * batch * heads * dk * (dv + mode) * 4 + n * heads * ((2 + mode) * dk * 2 + dv * 2 + dv * 4) + gates.numel() * 4
+    flops = 4.0 * n * heads * dk * dv
+    return _result("matrix_recurrence (exponential gates)" if mode else "matrix_recurrence (gated linear)", us, peaks,
+                   dict(tokens=tokens, batch=batch, heads=heads, dk=dk, dv=dv), nbytes, flops)
+
+
+def selective_scan(tokens=2048, batch=1, channels=4096, states=16, dt_rank=128, taps=4, iters=5, peaks=None):
+    from gllm_b200.ops import stateful
+
+    n = batch * tokens
+    xz = torch.randn(n, 2 * channels, device="cuda").to(torch.bfloat16)
+    xc = torch.randn(n, channels, device="cuda").to(torch.bfloat16)
+    proj = torch.randn(n, dt_rank + 2 * states, device="cuda").to(torch.bfloat16)
+    dt_raw = torch.randn(n, channels, device="cuda")
+    dt_b, D = torch.zeros(channels, device="cuda"), torch.ones(channels, device="cuda")
+    A = -torch.rand(channels, states, device="cuda") - 0.1
+    ssm = torch.zeros(batch + 1, channels, states, device="cuda")
+    conv = torch.zeros(batch + 1, taps - 1, channels, device="cuda")
+    b = _Batch(batch, tokens, 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: stateful.selective_scan(xc, dt_raw, dt_b, A, proj, dt_rank, dt_rank + states, D, xz, channels, ssm, conv,
+                                         taps, b.cu_q, b.state_slots, batch, max_q_len=tokens)
+    us = _time(fn, iters, flush)
+    nbytes = 2 * batch * channels * states * 4 + n * (channels * (2 + 4 + 2 + 2) + 2 * states * 2)
+    return _result("selective_scan", us, peaks, dict(tokens=tokens, batch=batch, channels=channels, states=states), nbytes,
+                   9.0 * n * channels * states)
+
+
+def conv_silu(tokens=2048, batch=1, channels=4096, taps=4, iters=5, peaks=None):
+    from gllm_b200.ops import stateful
+
+    n = batch * tokens
+    xz = torch.randn(n, 2 * channels, device="cuda").to(torch.bfloat16)
+    w, bias = torch.randn(channels, taps, device="cuda"), torch.zeros(channels, device="cuda")
+    conv = torch.zeros(batch + 1, taps - 1, channels, device="cuda")
+    b = _Batch(batch, tokens, 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: stateful.conv_silu(xz[:, :channels], w, bias, conv, b.positions, b.token_row), iters, flush)
+    return _result("conv_silu", us, peaks, dict(tokens=tokens, batch=batch, channels=channels, taps=taps),
+                   n * channels * 4)
+
+
+def stream_mix_norm(rows=2048, hidden=2048, streams=4, iters=5, peaks=None):
+    from gllm_b200.ops import stateful
+
+    resid = torch.randn(rows, streams * hidden, device="cuda")
+    y = torch.randn(rows, hidden, device="cuda").to(torch.bfloat16)
+    mix = torch.eye(streams, device="cuda").contiguous()
+    vec = torch.ones(streams, device="cuda")
+    weight = torch.ones(hidden, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: stateful.stream_mix_norm(y, resid, mix, vec, vec, weight, 1e-5, torch.bfloat16, streams), iters, flush)
+    return _result("stream_mix_norm", us, peaks, dict(rows=rows, hidden=hidden, streams=streams),
+                   rows * hidden * (8 * streams + 4))
+
+
 KERNELS = {
     "attention_decode": attention_decode,
     "attention_prefill": attention_prefill,
@@ -228,6 +362,11 @@ KERNELS = {
     "decode_step": decode_step,
     "add_rmsnorm": add_rmsnorm,
     "argmax": argmax,
+    "sigmoid_attention": sigmoid_attention,
+    "matrix_recurrence": matrix_recurrence,
+    "selective_scan": selective_scan,
+    "conv_silu": conv_silu,
+    "stream_mix_norm": stream_mix_norm,
 }
 
 

@@ -71,9 +71,9 @@ _SIGNATURES = {
     "recurrent": {
         "gllm_conv_silu_{t}": [P, c_int64, P, P, P, P, P, P, c_int, c_int, c_int, P],
         "gllm_selective_scan_{t}": [P, P, P, P, P, c_int64, c_int, c_int, P, P, c_int64, c_int, P, P, P, P, P, c_int,
-                                    c_int, c_int, c_int, P],
+                                    c_int, c_int, c_int, c_int, P],
         "gllm_matrix_recurrence_{t}": [c_int, P, c_int64, P, c_int64, P, c_int64, P, c_int64, P, P, c_float, c_float,
-                                       P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, P],
+                                       P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, P],
         "gllm_head_norm_{t}": [P, c_int64, c_int, c_int, c_float, P, c_int, P, c_int64, P, c_int64, c_int, c_int,
                                c_int, c_float, P],
     },

@@ -123,13 +123,14 @@ def conv_silu(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, 
 def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, A: torch.Tensor,
                    proj: torch.Tensor, b_offset: int, c_offset: int, D: torch.Tensor, xz: torch.Tensor,
                    z_offset: int, ssm_state: torch.Tensor, conv_state: torch.Tensor, taps: int,
-                   cu_q: torch.Tensor, state_slots: torch.Tensor, num_requests: int) -> torch.Tensor:
+                   cu_q: torch.Tensor, state_slots: torch.Tensor, num_requests: int, max_q_len: int = 0) -> torch.Tensor:
     """Per channel c and state n, token after token of each request:
     ``dt = softplus(dt_raw + dt_bias)``, ``S[c, n] = exp(dt A[c, n]) S[c, n] + dt x B[n]``,
     ``y = sum_n S[c, n] C[n] + D[c] x``, result ``y * silu(z)``.  ``B`` and ``C`` are the columns
     ``b_offset ..`` and ``c_offset ..`` of ``proj``, ``z`` the columns ``z_offset ..`` of ``xz`` whose
     first columns are the raw (unconvolved) inputs, the last ``taps-1`` of which become the new
-    ``conv_state``.  ``ssm_state [slots, channels, states]`` fp32 is updated in place."""
+    ``conv_state``.  ``ssm_state [slots, channels, states]`` fp32 is updated in place.  ``max_q_len`` 1 says
+    that every request brings one token: the kernel laid out for single tokens runs then."""
     _cuda(xc, "xc")
     _cuda(dt_raw, "dt_raw", torch.float32)
     _rows(proj, "proj", xc.dtype)
@@ -145,7 +146,7 @@ def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor
     _check(f(xc.data_ptr(), dt_raw.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), proj.data_ptr(), proj.stride(0),
              int(b_offset), int(c_offset), D.data_ptr(), xz.data_ptr(), xz.stride(0), int(z_offset),
              ssm_state.data_ptr(), conv_state.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), out.data_ptr(),
-             int(num_requests), channels, n_state, int(taps), _stream()), "selective_scan")
+             int(num_requests), int(max_q_len), channels, n_state, int(taps), _stream()), "selective_scan")
     return out
 
 
@@ -157,14 +158,16 @@ EXP_GATED = 1         # exponential input gate, log-sigmoid forget gate, running
 def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: torch.Tensor, gates: torch.Tensor,
                       gate_bias: torch.Tensor, lower: torch.Tensor | None, cap: float, q_scale: float,
                       state: torch.Tensor, mstate: torch.Tensor | None, cu_q: torch.Tensor,
-                      state_slots: torch.Tensor, num_requests: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+                      state_slots: torch.Tensor, num_requests: int, heads: int, dk: int, dv: int,
+                      max_q_len: int = 0) -> torch.Tensor:
     """``S <- diag(a) S + b v^T``, ``o = S^T q`` per (request, head), token after token.
     ``q, k [n, heads*dk]``, ``v [n, heads*dv]`` (rows may be slices), ``gates`` fp32 (``[n, heads*dk]``
     in mode ``GATED_LINEAR``, ``[n, 2*heads]`` = input | forget in mode ``EXP_GATED``).  ``state`` is
-    ``[slots, heads, dk, dv]`` (``dv + 1`` columns in mode ``EXP_GATED``: the last carries the
-    normaliser) and ``mstate [slots, heads]`` the running maximum.  Returns fp32
+    ``[slots, heads, dv, dk]``, one row per value column (``dv + 1`` rows in mode ``EXP_GATED``: the last
+    carries the normaliser) and ``mstate [slots, heads]`` the running maximum.  Returns fp32
     ``[n, heads * cols]``: ``cols = dv``, or ``dv + 2`` in mode ``EXP_GATED``, the two extra columns
-    being ``n . q`` and ``exp(-m)``."""
+    being ``n . q`` and ``exp(-m)``.  ``max_q_len`` 1 says that every request brings one token: the kernel laid
+    out for single tokens runs then."""
     _rows(q, "q")
     _rows(v, "v", q.dtype)
     if k is not None:
@@ -174,7 +177,7 @@ def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: tor
     _cuda(state, "state", torch.float32)
     n = q.shape[0]
     extra = 1 if mode == EXP_GATED else 0
-    if tuple(state.shape[1:]) != (heads, dk, dv + extra):
+    if tuple(state.shape[1:]) != (heads, dv + extra, dk):
         raise ValueError("the recurrence's state does not fit its heads")
     if mode == EXP_GATED:
         _cuda(mstate, "mstate", torch.float32)
@@ -184,11 +187,14 @@ def matrix_recurrence(mode: int, q: torch.Tensor, k: torch.Tensor | None, v: tor
         _cuda(lower, "lower", torch.float32)
     cols = dv + 2 * extra
     out = torch.empty((n, heads * cols), dtype=torch.float32, device=q.device)
+    # the scalar gates and the running maximum of every token, made by a small kernel before the recurrence
+    work = torch.empty((n, 4 * heads), dtype=torch.float32, device=q.device) if mode == EXP_GATED else None
     f = _fn("recurrent", f"gllm_matrix_recurrence_{_suffix(q.dtype)}")
     _check(f(int(mode), q.data_ptr(), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, v.data_ptr(),
              v.stride(0), gates.data_ptr(), gates.stride(0), gate_bias.data_ptr(), _ptr(lower), float(cap),
-             float(q_scale), state.data_ptr(), _ptr(mstate), cu_q.data_ptr(), state_slots.data_ptr(),
-             out.data_ptr(), out.stride(0), int(num_requests), heads, dk, dv, _stream()), "matrix_recurrence")
+             float(q_scale), state.data_ptr(), _ptr(mstate), _ptr(work), cu_q.data_ptr(), state_slots.data_ptr(),
+             out.data_ptr(), out.stride(0), int(num_requests), int(max_q_len), heads, dk, dv, _stream()),
+           "matrix_recurrence")
     return out
 
 
@@ -288,8 +294,8 @@ def _sigmoid_attention_mma(qkv, cache_pages, block_table, head_bias, heads, kv_h
     tiles = -(-batch.max_q_len // qt) * head_tiles * batch.num_requests
     sms = torch.cuda.get_device_properties(qkv.device).multi_processor_count
     splits, tiles_per_split = 1, 0
-    if tiles < sms and batch.max_seq_len > 2 * SPLIT_KEYS:
-        want = min(MAX_SPLITS, -(-2 * sms // tiles))
+    if tiles < 4 * sms and batch.max_seq_len > 2 * SPLIT_KEYS:
+        want = min(MAX_SPLITS, -(-8 * sms // tiles))          # five CTAs fit an SM: keep them all streaming
         tiles_per_split = max(SPLIT_KEYS // 64, -(-(-(-batch.max_seq_len // 64)) // want))
         splits = -(-(-(-batch.max_seq_len // 64)) // tiles_per_split)
     partial = None

@@ -67,5 +67,5 @@ class SelectiveScanMixer(Mixer):
         dt_raw = ops.linear(proj[:, : self.dt_rank], self.w_dt, out_dtype=torch.float32)
         y = stateful.selective_scan(xc, dt_raw, self.dt_b, self.A, proj, self.dt_rank, self.dt_rank + self.n_state,
                                     self.D, xz, self.inner, ssm_state, conv_state, self.taps, ctx.cu_q,
-                                    ctx.state_slots, ctx.num_requests)
+                                    ctx.state_slots, ctx.num_requests, max_q_len=ctx.max_q_len)
         return ops.linear(y, self.w_o, split_ok=True, add_into=getattr(ctx, "residual_sink", None))

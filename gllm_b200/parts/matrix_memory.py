@@ -43,7 +43,7 @@ class GatedLinearAttention(Mixer):
         return {"modules": {"recurrent"}}
 
     def state_requirement(self):
-        return StateRequirement((self.heads, self.dk, self.dv), torch.float32)
+        return StateRequirement((self.heads, self.dv, self.dk), torch.float32)
 
     def expected_tensors(self):
         n, hk, hv = self.names, self.heads * self.dk, self.heads * self.dv
@@ -69,7 +69,7 @@ class GatedLinearAttention(Mixer):
         gates = ops.linear(x, self.w_f, out_dtype=torch.float32)      # the gate of the recurrence stays fp32
         o = stateful.matrix_recurrence(stateful.GATED_LINEAR, qv[:, :hk], None, qv[:, hk:], gates, self.f_bias,
                                        self.lower, 0.0, 1.0, cache.states[0], None, ctx.cu_q, ctx.state_slots,
-                                       ctx.num_requests, self.heads, self.dk, self.dv)
+                                       ctx.num_requests, self.heads, self.dk, self.dv, max_q_len=ctx.max_q_len)
         normed = stateful.head_norm(o, self.heads, self.dv, self.norm, self.eps, x.dtype)
         return ops.linear(normed, self.w_o, split_ok=True, add_into=getattr(ctx, "residual_sink", None))
 
@@ -90,8 +90,8 @@ class ExpGatedMemory(Mixer):
         return {"modules": {"recurrent"}}
 
     def state_requirement(self):
-        # the memory with its normaliser as one more column, and the running maximum
-        return (StateRequirement((self.heads, self.dk, self.dv + 1), torch.float32),
+        # the memory, column by column, with its normaliser as one more column, and the running maximum
+        return (StateRequirement((self.heads, self.dv + 1, self.dk), torch.float32),
                 StateRequirement((self.heads,), torch.float32))
 
     def expected_tensors(self):
@@ -123,7 +123,7 @@ class ExpGatedMemory(Mixer):
         memory, maximum = cache.states
         o = stateful.matrix_recurrence(stateful.EXP_GATED, qkvg[:, :hk], qkvg[:, hk:2 * hk], qkvg[:, 2 * hk:2 * hk + hv],
                                        gates, self.if_bias, None, self.gate_cap, self.dk ** -0.5, memory, maximum,
-                                       ctx.cu_q, ctx.state_slots, ctx.num_requests, self.heads, self.dk, self.dv)
+                                       ctx.cu_q, ctx.state_slots, ctx.num_requests, self.heads, self.dk, self.dv, max_q_len=ctx.max_q_len)
         normed = stateful.head_norm(o, self.heads, self.dv, self.norm, self.eps, x.dtype, with_denominator=True,
                                     denominator_eps=self.DENOMINATOR_EPS, gate=qkvg[:, 2 * hk + hv:])
         return ops.linear(normed, self.w_o, split_ok=True, add_into=getattr(ctx, "residual_sink", None))
