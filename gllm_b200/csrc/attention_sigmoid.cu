@@ -118,6 +118,11 @@ attention_sigmoid_kernel(const T* __restrict__ q, int64_t q_stride, T* __restric
         vbase = (int64_t)((size_t)page * page_elems + v_base + ((size_t)kvh * block_size + off) * dv);
       }
     }
+    // the block's 32 terms are added up by themselves and then added to the total: the rounding error of a
+    // long context grows with the number of blocks, not with the number of keys
+    float part[MAX_DV / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_DV / 32; ++i) part[i] = 0.f;
     const int count = min(32, qpos - j0 + 1);
     for (int jj = 0; jj < count; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
@@ -127,9 +132,11 @@ attention_sigmoid_kernel(const T* __restrict__ q, int64_t q_stride, T* __restric
 #pragma unroll
       for (int i = 0; i < MAX_DV / 32; ++i) {
         const int c = lane + 32 * i;
-        if (c < dv) acc[i] = fmaf(pj, to_float(vp[c]), acc[i]);
+        if (c < dv) part[i] = fmaf(pj, to_float(vp[c]), part[i]);
       }
     }
+#pragma unroll
+    for (int i = 0; i < MAX_DV / 32; ++i) acc[i] += part[i];
   }
   T* o = out + (int64_t)n * out_stride + (int64_t)h * dv;
 #pragma unroll
