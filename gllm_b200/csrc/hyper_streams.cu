@@ -43,15 +43,16 @@ embed_streams_kernel(const int* __restrict__ tokens, const int* __restrict__ sam
 }
 
 // rows == nullptr: token i = blockIdx.x, X is updated in place.  rows given: only those tokens, X untouched.
-template <typename T>
+template <typename T, int STREAMS>
 __global__ void __launch_bounds__(256)
 stream_mix_norm_kernel(const T* __restrict__ y, float* __restrict__ X, const float* __restrict__ mix,
                        const float* __restrict__ write, const float* __restrict__ read,
                        const float* __restrict__ weight, T* __restrict__ out, float* __restrict__ sum_out,
-                       const int* __restrict__ rows, int width, int streams, float eps) {
+                       const int* __restrict__ rows, int width, float eps) {
+  constexpr int streams = STREAMS;
   extern __shared__ float u_s[];          // [width]
   __shared__ float scratch[32];
-  __shared__ float mix_s[MAX_STREAMS * MAX_STREAMS], write_s[MAX_STREAMS], read_s[MAX_STREAMS];
+  __shared__ float mix_s[STREAMS * STREAMS], write_s[STREAMS], read_s[STREAMS];
   if (threadIdx.x < streams * streams) mix_s[threadIdx.x] = mix ? mix[threadIdx.x] : 0.f;
   if (threadIdx.x < streams) {
     write_s[threadIdx.x] = write ? write[threadIdx.x] : 0.f;
@@ -64,32 +65,45 @@ stream_mix_norm_kernel(const T* __restrict__ y, float* __restrict__ X, const flo
   float* x = X + (int64_t)i * streams * width;
   const bool has_y = y != nullptr;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float old[MAX_STREAMS];
+  // four columns a thread at a time: all their loads are asked for before the first store (the streams are
+  // read and written through the same pointer, so the compiler keeps loads behind earlier stores)
+  constexpr int UNROLL = 4;
+  for (int c0 = threadIdx.x; c0 < width; c0 += UNROLL * blockDim.x) {
+    float old[UNROLL][STREAMS], yv[UNROLL];
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) old[s] = s < streams ? x[(int64_t)s * width + c] : 0.f;
-    float u = 0.f;
-    if (has_y) {
-      const float yv = to_float(y[(int64_t)i * width + c]);
+    for (int k = 0; k < UNROLL; ++k) {
+      const int c = c0 + k * blockDim.x;
+      const bool ok = c < width;
 #pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t) {
-        if (t < streams) {
-          float nv = 0.f;
-#pragma unroll
-          for (int s = 0; s < MAX_STREAMS; ++s)
-            if (s < streams) nv = fmaf(mix_s[s * streams + t], old[s], nv);
-          nv = fmaf(write_s[t], yv, nv);
-          if (!rows) x[(int64_t)t * width + c] = nv;
-          u = fmaf(read_s[t], nv, u);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int t = 0; t < MAX_STREAMS; ++t)
-        if (t < streams) u = fmaf(read_s[t], old[t], u);
+      for (int s = 0; s < STREAMS; ++s) old[k][s] = (ok && s < streams) ? x[(int64_t)s * width + c] : 0.f;
+      yv[k] = (ok && has_y) ? to_float(y[(int64_t)i * width + c]) : 0.f;
     }
-    u_s[c] = u;
-    ss = fmaf(u, u, ss);
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      const int c = c0 + k * blockDim.x;
+      if (c >= width) break;
+      float u = 0.f;
+      if (has_y) {
+#pragma unroll
+        for (int t = 0; t < STREAMS; ++t) {
+          if (t < streams) {
+            float nv = 0.f;
+#pragma unroll
+            for (int s = 0; s < STREAMS; ++s)
+              if (s < streams) nv = fmaf(mix_s[s * streams + t], old[k][s], nv);
+            nv = fmaf(write_s[t], yv[k], nv);
+            if (!rows) x[(int64_t)t * width + c] = nv;
+            u = fmaf(read_s[t], nv, u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < STREAMS; ++t)
+          if (t < streams) u = fmaf(read_s[t], old[k][t], u);
+      }
+      u_s[c] = u;
+      ss = fmaf(u, u, ss);
+    }
   }
   if (sum_out) {
     for (int c = threadIdx.x; c < width; c += blockDim.x) sum_out[(int64_t)blockIdx.x * width + c] = u_s[c];
@@ -119,12 +133,24 @@ int stream_mix_norm_launch(const T* y, float* X, const float* mix, const float* 
   if (streams < 1 || streams > MAX_STREAMS || width < 1 || (size_t)width * 4 > 160 * 1024)
     return (int)cudaErrorInvalidValue;
   const size_t smem = (size_t)width * sizeof(float);
+  void (*kernel)(const T*, float*, const float*, const float*, const float*, const float*, T*, float*, const int*, int,
+                 float) = nullptr;
+  switch (streams) {
+    case 1: kernel = stream_mix_norm_kernel<T, 1>; break;
+    case 2: kernel = stream_mix_norm_kernel<T, 2>; break;
+    case 3: kernel = stream_mix_norm_kernel<T, 3>; break;
+    case 4: kernel = stream_mix_norm_kernel<T, 4>; break;
+    case 5: kernel = stream_mix_norm_kernel<T, 5>; break;
+    case 6: kernel = stream_mix_norm_kernel<T, 6>; break;
+    case 7: kernel = stream_mix_norm_kernel<T, 7>; break;
+    default: kernel = stream_mix_norm_kernel<T, 8>; break;
+  }
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(stream_mix_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return gllm_launch(stream_mix_norm_kernel<T>, dim3(n_rows), dim3(256), smem, stream, y, X, mix, write, read, weight,
-                     out, sum_out, rows, width, streams, eps);
+  return gllm_launch(kernel, dim3(n_rows), dim3(256), smem, stream, y, X, mix, write, read, weight, out, sum_out, rows,
+                     width, eps);
 }
 }  // namespace
 

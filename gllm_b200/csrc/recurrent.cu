@@ -21,16 +21,21 @@ __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.f) - 
 // Loads that stay where they are written: the look-ahead of the chunked kernels below asks for the next chunk's
 // inputs before it computes the current one, and the compiler would otherwise move the loads down to their first
 // use, behind the computation they are meant to overlap.
-__device__ __forceinline__ float load_ahead(const float* p) {
-  float v;
-  asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+// They return the loaded bits untouched (a bfloat16 zero-extended by the load itself): any instruction on the value,
+// even the shift that makes a float of a bfloat16, would wait for the load right there.  as_value() is for later.
+__device__ __forceinline__ uint32_t load_ahead(const float* p) {
+  uint32_t v;
+  asm volatile("ld.global.b32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
-__device__ __forceinline__ float load_ahead(const __nv_bfloat16* p) {
-  unsigned short u;
-  asm volatile("ld.global.u16 %0, [%1];" : "=h"(u) : "l"(p));
-  return __uint_as_float(((unsigned int)u) << 16);
+__device__ __forceinline__ uint32_t load_ahead(const __nv_bfloat16* p) {
+  uint32_t v;
+  asm volatile("ld.global.u16 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
 }
+template <typename T> __device__ __forceinline__ float as_value(uint32_t bits);
+template <> __device__ __forceinline__ float as_value<float>(uint32_t bits) { return __uint_as_float(bits); }
+template <> __device__ __forceinline__ float as_value<__nv_bfloat16>(uint32_t bits) { return __uint_as_float(bits << 16); }
 
 // --------------------------------------------------------------- causal convolution + SiLU
 // out[i, c] = silu(bias[c] + sum_j w[c, taps-1-j] * x[i-j, c]) over the request's own earlier tokens;
@@ -79,13 +84,14 @@ conv_silu_kernel(const T* __restrict__ x, int64_t x_stride, const float* __restr
 // The tokens of a request are taken in chunks of `tc`: while one chunk is computed from shared memory,
 // the inputs of the next (step size, input and gate of every channel of the block, B and C rows) are
 // already on their way from global memory into registers, and go into the other buffer afterwards.
-constexpr int SCAN_THREADS = 128;
+// Blocks are large (512 threads) when there are channels enough: the warps of a block hide one another's
+// latencies, and a block's B and C rows are staged once for all its channels.
 constexpr int SCAN_MAX_CHUNK = 16;
-constexpr int SCAN_PF_BC = 8;      // B/C values a thread fetches ahead per chunk: tc * 2 * n_state <= 128 * 8
-constexpr int SCAN_PF_CH = 8;      // (token, channel) cells a thread fetches ahead: tc * channels per block <= 128 * 8
+constexpr int SCAN_PF_BC = 8;      // B/C values a thread fetches ahead per chunk: tc * 2 * n_state <= threads * 8
+constexpr int SCAN_PF_CH = 8;      // (token, channel) cells a thread fetches ahead: tc * channels per block <= threads * 8
 
-template <typename T, int NPT>
-__global__ void __launch_bounds__(SCAN_THREADS)
+template <typename T, int NPT, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  convolved, activated input
                       const float* __restrict__ dt_raw,    // [n, channels]  step-size projection, before bias
                       const float* __restrict__ dt_bias,   // [channels]
@@ -102,7 +108,7 @@ selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  con
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.y;
-  const int per_block = SCAN_THREADS / lanes;
+  const int per_block = THREADS / lanes;
   const int c0 = blockIdx.x * per_block;
   const int cl = threadIdx.x / lanes;            // channel within the block
   const int c = c0 + cl;
@@ -124,30 +130,29 @@ selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  con
   }
   const float dskip = D[cc];
 
-  float pf_bc[SCAN_PF_BC], pf_dt[SCAN_PF_CH], pf_x[SCAN_PF_CH], pf_z[SCAN_PF_CH];
+  uint32_t pf_bc[SCAN_PF_BC], pf_dt[SCAN_PF_CH], pf_x[SCAN_PF_CH], pf_z[SCAN_PF_CH];
+  const int ch_mine = c0 + (threadIdx.x & (per_block - 1)), tt_c0 = threadIdx.x / per_block;   // per_block * lanes = THREADS
+  const float bias_mine = ch_mine < channels ? dt_bias[ch_mine] : 0.f;
   auto fetch = [&](int t0, int nt) {
 #pragma unroll
     for (int j = 0; j < SCAN_PF_BC; ++j) {
-      const int idx = threadIdx.x + j * SCAN_THREADS;
-      if (idx < nt * 2 * n_state) {
-        const int tt = idx / (2 * n_state), n = idx - tt * 2 * n_state;
-        const T* row = bc + (int64_t)(t0 + tt) * bc_stride;
-        pf_bc[j] = load_ahead(n < n_state ? row + b_off + n : row + c_off + n - n_state);
-      }
+      const int idx = threadIdx.x + j * THREADS;
+      if (idx >= nt * 2 * n_state) break;
+      const int tt = idx / (2 * n_state), n = idx - tt * 2 * n_state;
+      const T* row = bc + (int64_t)(t0 + tt) * bc_stride;
+      pf_bc[j] = load_ahead(n < n_state ? row + b_off + n : row + c_off + n - n_state);
     }
+    // a thread keeps one channel of the block and walks the chunk's tokens in steps of `lanes`
 #pragma unroll
     for (int j = 0; j < SCAN_PF_CH; ++j) {
-      const int idx = threadIdx.x + j * SCAN_THREADS;
-      if (idx < nt * per_block) {
-        const int tt = idx / per_block, ch = c0 + idx - tt * per_block;
-        if (ch < channels) {
-          const int64_t t = t0 + tt;
-          pf_dt[j] = load_ahead(dt_raw + t * channels + ch) + dt_bias[ch];
-          pf_x[j] = load_ahead(xc + t * channels + ch);
-          pf_z[j] = load_ahead(xz + t * xz_stride + z_off + ch);
-        } else {
-          pf_dt[j] = pf_x[j] = pf_z[j] = 0.f;
-        }
+      const int tt = tt_c0 + j * lanes;
+      if (tt >= nt) break;
+      pf_dt[j] = pf_x[j] = pf_z[j] = 0u;
+      if (ch_mine < channels) {
+        const int64_t t = t0 + tt;
+        pf_dt[j] = load_ahead(dt_raw + t * channels + ch_mine);
+        pf_x[j] = load_ahead(xc + t * channels + ch_mine);
+        pf_z[j] = load_ahead(xz + t * xz_stride + z_off + ch_mine);
       }
     }
   };
@@ -158,17 +163,18 @@ selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  con
     float* z_s = x_s + tc * per_block;
 #pragma unroll
     for (int j = 0; j < SCAN_PF_BC; ++j) {
-      const int idx = threadIdx.x + j * SCAN_THREADS;
-      if (idx < nt * 2 * n_state) bc_s[idx] = pf_bc[j];
+      const int idx = threadIdx.x + j * THREADS;
+      if (idx >= nt * 2 * n_state) break;
+      bc_s[idx] = as_value<T>(pf_bc[j]);
     }
 #pragma unroll
     for (int j = 0; j < SCAN_PF_CH; ++j) {
-      const int idx = threadIdx.x + j * SCAN_THREADS;
-      if (idx < nt * per_block) {
-        dt_s[idx] = softplusf_(pf_dt[j]);
-        x_s[idx] = pf_x[j];
-        z_s[idx] = siluf_(pf_z[j]);
-      }
+      const int tt = tt_c0 + j * lanes;
+      if (tt >= nt) break;
+      const int idx = tt * per_block + (threadIdx.x & (per_block - 1));
+      dt_s[idx] = softplusf_(as_value<float>(pf_dt[j]) + bias_mine);
+      x_s[idx] = as_value<T>(pf_x[j]);
+      z_s[idx] = siluf_(as_value<T>(pf_z[j]));
     }
   };
 
@@ -300,10 +306,12 @@ exp_gate_scan_kernel(const float* __restrict__ gates, int64_t gates_stride, cons
 // key) and v and put into the other buffer afterwards.
 constexpr int REC_THREADS = 256;
 constexpr int REC_MAX_CHUNK = 16;
-constexpr int REC_PF = 8;          // look-ahead registers per operand: tc * lanes * DPT <= 256 * 8, tc * cols <= 256 * 8
+constexpr int REC_LOOKAHEAD = 2048; // values of one operand that a block fetches ahead per chunk (8 per thread)
+// (Blocks of 1,024 threads, which would activate a chunk's q and gate once for 64 columns instead of once per 16,
+// measured the same or slower: 8 warps per scheduler then wait for issue slots instead of for one another.)
 
-template <typename T, int DPT>
-__global__ void __launch_bounds__(REC_THREADS)
+template <typename T, int DPT, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 matrix_recurrence_kernel(int mode,
                          const T* __restrict__ q, int64_t q_stride,       // [n, heads * dk] at its offset
                          const T* __restrict__ k, int64_t k_stride,       // mode 1
@@ -317,10 +325,11 @@ matrix_recurrence_kernel(int mode,
                          const int* __restrict__ cu_q, const int* __restrict__ state_slots,
                          float* __restrict__ out, int64_t out_stride,     // [n, heads * out_cols]
                          int heads, int dk, int dv, int lanes, int tc) {
+  constexpr int PF = REC_LOOKAHEAD / THREADS;
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
-  const int cols = REC_THREADS / lanes;
+  const int cols = THREADS / lanes;
   const int dkp = lanes * DPT;                 // padded row of the staged operands
   const int dvx = dv + (mode == 1 ? 1 : 0);
   const int out_cols = dv + (mode == 1 ? 2 : 0);
@@ -343,29 +352,50 @@ matrix_recurrence_kernel(int mode,
     S[i] = (live && d < dk) ? sp[d] : 0.f;
   }
 
-  float pq[REC_PF], pg[REC_PF], pv[REC_PF], pi = 0.f, pf = 0.f, pmp = 0.f, pmn = 0.f;
+  uint32_t pq[PF], pg[PF], pv[PF], pi = 0u, pf = 0u, pmp = 0u, pmn = 0u;
+  // Which cells of a chunk a thread fetches does not change from chunk to chunk.  With dkp <= THREADS (both powers
+  // of two) a thread keeps one key channel and walks the tokens in steps of THREADS / dkp: no division per cell,
+  // and a thread stops at the chunk's end instead of running through its dead look-ahead slots.
+  const bool fast = dkp <= THREADS;
+  const int d_mine = threadIdx.x & (dkp - 1), tt_q0 = threadIdx.x / dkp, tt_qstep = fast ? THREADS / dkp : 0;
+  const int c_mine = threadIdx.x & (cols - 1), tt_v0 = threadIdx.x / cols, tt_vstep = lanes;   // THREADS / cols
+  const int hd_mine = h * dk + min(d_mine, dk - 1);
+  const int cg_mine = blockIdx.x * cols + c_mine;
+  const float lo_mine = (mode == 0 && fast && d_mine < dk) ? lower[hd_mine] : 0.f;
+  const float gb_mine = (mode == 0 && fast && d_mine < dk) ? gate_bias[hd_mine] : 0.f;
   auto fetch = [&](int t0, int nt) {
+    if (fast) {
 #pragma unroll
-    for (int j = 0; j < REC_PF; ++j) {
-      const int idx = threadIdx.x + j * REC_THREADS;
-      if (idx < nt * dkp) {
+      for (int j = 0; j < PF; ++j) {
+        const int tt = tt_q0 + j * tt_qstep;
+        if (tt >= nt) break;
+        pq[j] = pg[j] = 0u;
+        if (d_mine < dk) {
+          const int64_t t = t0 + tt;
+          pq[j] = load_ahead(q + t * q_stride + hd_mine);
+          pg[j] = mode == 1 ? load_ahead(k + t * k_stride + hd_mine) : load_ahead(gates + t * gates_stride + hd_mine);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < PF; ++j) {
+        const int idx = threadIdx.x + j * THREADS;
+        if (idx >= nt * dkp) break;
         const int tt = idx / dkp, d = idx - tt * dkp;
-        pq[j] = pg[j] = 0.f;
+        pq[j] = pg[j] = 0u;
         if (d < dk) {
           const int64_t t = t0 + tt;
           const int hd = h * dk + d;
           pq[j] = load_ahead(q + t * q_stride + hd);
-          pg[j] = mode == 1 ? load_ahead(k + t * k_stride + hd) : load_ahead(gates + t * gates_stride + hd) + gate_bias[hd];
+          pg[j] = mode == 1 ? load_ahead(k + t * k_stride + hd) : load_ahead(gates + t * gates_stride + hd);
         }
       }
     }
 #pragma unroll
-    for (int j = 0; j < REC_PF; ++j) {
-      const int idx = threadIdx.x + j * REC_THREADS;
-      if (idx < nt * cols) {
-        const int tt = idx / cols, cg = blockIdx.x * cols + idx - tt * cols;
-        pv[j] = cg < dv ? load_ahead(v + (int64_t)(t0 + tt) * v_stride + (int64_t)h * dv + cg) : 1.0f;
-      }
+    for (int j = 0; j < PF; ++j) {
+      const int tt = tt_v0 + j * tt_vstep;
+      if (tt >= nt) break;
+      pv[j] = cg_mine < dv ? load_ahead(v + (int64_t)(t0 + tt) * v_stride + (int64_t)h * dv + cg_mine) : 0u;
     }
     if (mode == 1 && (int)threadIdx.x < nt) {
       const float* g = gates + (int64_t)(t0 + threadIdx.x) * gates_stride;
@@ -380,30 +410,48 @@ matrix_recurrence_kernel(int mode,
     float* g_s = buf + tc * dkp;
     float* v_s = g_s + tc * dkp;
     float* sc_s = v_s + tc * cols;
+    if (fast) {
 #pragma unroll
-    for (int j = 0; j < REC_PF; ++j) {
-      const int idx = threadIdx.x + j * REC_THREADS;
-      if (idx < nt * dkp) {
+      for (int j = 0; j < PF; ++j) {
+        const int tt = tt_q0 + j * tt_qstep;
+        if (tt >= nt) break;
+        const int idx = tt * dkp + d_mine;
+        if (mode == 1) {
+          q_s[idx] = as_value<T>(pq[j]) * q_scale;
+          g_s[idx] = as_value<T>(pg[j]);
+        } else {
+          q_s[idx] = d_mine < dk ? siluf_(as_value<T>(pq[j])) : 0.f;
+          g_s[idx] = d_mine < dk ? lo_mine + (1.0f - lo_mine) * sigmoidf_(as_value<float>(pg[j]) + gb_mine) : 0.f;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < PF; ++j) {
+        const int idx = threadIdx.x + j * THREADS;
+        if (idx >= nt * dkp) break;
         const int d = idx % dkp;
         if (mode == 1) {
-          q_s[idx] = pq[j] * q_scale;
-          g_s[idx] = pg[j];
+          q_s[idx] = as_value<T>(pq[j]) * q_scale;
+          g_s[idx] = as_value<T>(pg[j]);
         } else {
           const float lo = d < dk ? lower[h * dk + d] : 0.f;
-          q_s[idx] = d < dk ? siluf_(pq[j]) : 0.f;
-          g_s[idx] = d < dk ? lo + (1.0f - lo) * sigmoidf_(pg[j]) : 0.f;
+          const float bias = d < dk ? gate_bias[h * dk + d] : 0.f;
+          q_s[idx] = d < dk ? siluf_(as_value<T>(pq[j])) : 0.f;
+          g_s[idx] = d < dk ? lo + (1.0f - lo) * sigmoidf_(as_value<float>(pg[j]) + bias) : 0.f;
         }
       }
     }
 #pragma unroll
-    for (int j = 0; j < REC_PF; ++j) {
-      const int idx = threadIdx.x + j * REC_THREADS;
-      if (idx < nt * cols) v_s[idx] = pv[j];
+    for (int j = 0; j < PF; ++j) {
+      const int tt = tt_v0 + j * tt_vstep;
+      if (tt >= nt) break;
+      v_s[tt * cols + c_mine] = cg_mine < dv ? as_value<T>(pv[j]) : 1.0f;
     }
     if (mode == 1 && (int)threadIdx.x < nt) {
-      sc_s[threadIdx.x] = expf(pf + pmp - pmn);          // keep
-      sc_s[tc + threadIdx.x] = expf(pi - pmn);           // take
-      sc_s[2 * tc + threadIdx.x] = expf(-pmn);
+      const float m_new = as_value<float>(pmn);
+      sc_s[threadIdx.x] = expf(as_value<float>(pf) + as_value<float>(pmp) - m_new);          // keep
+      sc_s[tc + threadIdx.x] = expf(as_value<float>(pi) - m_new);                            // take
+      sc_s[2 * tc + threadIdx.x] = expf(-m_new);
     }
   };
 
@@ -681,17 +729,25 @@ int selective_scan_launch(const T* xc, const float* dt_raw, const float* dt_bias
   const int npt = n_state <= 64 ? 2 : 8;
   const int lanes = pow2_at_least((n_state + npt - 1) / npt);
   if (lanes > 32 || taps < 1 || taps > MAX_TAPS || num_requests > 65535) return (int)cudaErrorInvalidValue;
-  const int per_block = SCAN_THREADS / lanes;
-  // tokens per chunk: as many as a thread's look-ahead registers hold of the chunk's B and C values
+  const int threads = (int64_t)channels * lanes >= 4096 ? 512 : 128;
+  const int per_block = threads / lanes;
+  // tokens per chunk: as many as a thread's look-ahead registers hold of the chunk's values
   int tc = SCAN_MAX_CHUNK;
-  while (tc > 1 && (tc * 2 * n_state > SCAN_THREADS * SCAN_PF_BC || tc * per_block > SCAN_THREADS * SCAN_PF_CH)) tc >>= 1;
-  if (tc * 2 * n_state > SCAN_THREADS * SCAN_PF_BC || tc * per_block > SCAN_THREADS * SCAN_PF_CH)
+  while (tc > 1 && (tc * 2 * n_state > threads * SCAN_PF_BC || tc * per_block > threads * SCAN_PF_CH)) tc >>= 1;
+  if (tc * 2 * n_state > threads * SCAN_PF_BC || tc * per_block > threads * SCAN_PF_CH)
     return (int)cudaErrorInvalidValue;
   const size_t smem = 2 * sizeof(float) * (size_t)tc * (2 * n_state + 3 * per_block);
-  auto kernel = npt == 2 ? selective_scan_kernel<T, 2> : selective_scan_kernel<T, 8>;
-  return gllm_launch(kernel, dim3((channels + per_block - 1) / per_block, num_requests),
-                     dim3(SCAN_THREADS), smem, stream, xc, dt_raw, dt_bias, A, bc, bc_stride, b_off, c_off, D, xz,
-                     xz_stride, z_off, ssm_state, conv_state, cu_q, state_slots, out, channels, n_state, taps, lanes, tc);
+  void (*kernel)(const T*, const float*, const float*, const float*, const T*, int64_t, int, int, const float*, const T*,
+                 int64_t, int, float*, float*, const int*, const int*, T*, int, int, int, int, int);
+  if (threads == 512) kernel = npt == 2 ? selective_scan_kernel<T, 2, 512> : selective_scan_kernel<T, 8, 512>;
+  else kernel = npt == 2 ? selective_scan_kernel<T, 2, 128> : selective_scan_kernel<T, 8, 128>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return gllm_launch(kernel, dim3((channels + per_block - 1) / per_block, num_requests), dim3(threads), smem, stream, xc,
+                     dt_raw, dt_bias, A, bc, bc_stride, b_off, c_off, D, xz, xz_stride, z_off, ssm_state, conv_state, cu_q,
+                     state_slots, out, channels, n_state, taps, lanes, tc);
 }
 
 template <typename T>
@@ -721,19 +777,23 @@ int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k,
   }
   const int dpt = dk <= 128 ? 4 : 16;
   int lanes = pow2_at_least((dk + dpt - 1) / dpt);
-  if (lanes < 2) lanes = 2;                      // at most 128 columns per block
-  const int cols = REC_THREADS / lanes;
+  if (lanes < 2) lanes = 2;
+  const int threads = REC_THREADS;
+  const int cols = threads / lanes;
   const int dkp = lanes * dpt;
   int tc = REC_MAX_CHUNK;
-  while (tc > 1 && (tc * dkp > REC_THREADS * REC_PF || tc * cols > REC_THREADS * REC_PF)) tc >>= 1;
+  while (tc > 1 && (tc * dkp > REC_LOOKAHEAD || tc * cols > REC_LOOKAHEAD)) tc >>= 1;
+  if (tc * dkp > REC_LOOKAHEAD || tc * cols > REC_LOOKAHEAD) return (int)cudaErrorInvalidValue;
   const size_t smem = sizeof(float) * 2 * (size_t)tc * (2 * dkp + cols + 4);
-  auto kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4> : matrix_recurrence_kernel<T, 16>;
+  void (*kernel)(int, const T*, int64_t, const T*, int64_t, const T*, int64_t, const float*, int64_t, const float*,
+                 const float*, float, float*, const int*, const int*, float*, int64_t, int, int, int, int, int);
+  kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS> : matrix_recurrence_kernel<T, 16, REC_THREADS>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return gllm_launch(kernel, dim3((dvx + cols - 1) / cols, heads, num_requests), dim3(REC_THREADS), smem, stream, mode,
-                     q, q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias, lower, q_scale, state, cu_q,
+  return gllm_launch(kernel, dim3((dvx + cols - 1) / cols, heads, num_requests), dim3(threads), smem, stream, mode, q,
+                     q_stride, k, k_stride, v, v_stride, gates, gates_stride, gate_bias, lower, q_scale, state, cu_q,
                      state_slots, out, out_stride, heads, dk, dv, lanes, tc);
 }
 
