@@ -210,8 +210,11 @@ selective_scan_kernel(const T* __restrict__ xc,            // [n, channels]  con
           y = fmaf(S[k], brow[n_state + n], y);
         }
       }
-      for (int o = lanes >> 1; o > 0; o >>= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
-      if (sub == 0 && live) out_p[(int64_t)tt * channels] = from_float<T>((y + dskip * x) * z_s[tt * per_block + cl]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+        if (o < lanes) y += __shfl_xor_sync(0xffffffffu, y, o);          // (lanes is the same for the whole grid)
+      if (sub == 0 && live) *out_p = from_float<T>((y + dskip * x) * z_s[tt * per_block + cl]);
+      out_p += channels;
     }
     if (next < end) stash(nt_next, scan_smem + (which ^ 1) * buf_floats);
     __syncthreads();
@@ -300,7 +303,7 @@ exp_gate_scan_kernel(const float* __restrict__ gates, int64_t gates_stride, cons
 // has one column more than there are value columns, fed with ones, which carries the normaliser n, and
 // the output gets two columns more: n . q and exp(-m').
 // A block owns `cols` columns of one (request, head); `lanes` threads share a column, each keeping DPT of its
-// key channels (4 for up to 128 key channels, 16 beyond: the recurrence is a chain from token to token, bounded
+// key channels (4 for up to 128 key channels, 16 beyond; 8 for 65..128 measured the same: the recurrence is a chain from token to token, bounded
 // by the instructions a warp spends per token, so the state is spread over many threads).  Tokens are taken in chunks of `tc`: while a chunk is computed from shared memory, the raw
 // inputs of the next one are on their way into registers; they are turned into the effective q, gate (or
 // key) and v and put into the other buffer afterwards.
@@ -310,9 +313,9 @@ constexpr int REC_LOOKAHEAD = 2048; // values of one operand that a block fetche
 // (Blocks of 1,024 threads, which would activate a chunk's q and gate once for 64 columns instead of once per 16,
 // measured the same or slower: 8 warps per scheduler then wait for issue slots instead of for one another.)
 
-template <typename T, int DPT, int THREADS>
+template <typename T, int DPT, int THREADS, int MODE>
 __global__ void __launch_bounds__(THREADS)
-matrix_recurrence_kernel(int mode,
+matrix_recurrence_kernel(int,
                          const T* __restrict__ q, int64_t q_stride,       // [n, heads * dk] at its offset
                          const T* __restrict__ k, int64_t k_stride,       // mode 1
                          const T* __restrict__ v, int64_t v_stride,       // [n, heads * dv]
@@ -326,6 +329,7 @@ matrix_recurrence_kernel(int mode,
                          float* __restrict__ out, int64_t out_stride,     // [n, heads * out_cols]
                          int heads, int dk, int dv, int lanes, int tc) {
   constexpr int PF = REC_LOOKAHEAD / THREADS;
+  constexpr int mode = MODE;
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   pdl_wait();
@@ -496,9 +500,12 @@ matrix_recurrence_kernel(int mode,
           o = fmaf(S[i], qa[e], o);
         }
       }
-      for (int off = lanes >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-      if (sub == 0 && live) out_p[(int64_t)tt * out_stride + col] = o;
-      if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) out_p[(int64_t)tt * out_stride + dv + 1] = sc_s[2 * tc + tt];
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1)
+        if (off < lanes) o += __shfl_xor_sync(0xffffffffu, o, off);      // (lanes is the same for the whole grid)
+      if (sub == 0 && live) out_p[col] = o;
+      if (mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) out_p[dv + 1] = sc_s[2 * tc + tt];
+      out_p += out_stride;
     }
     if (next < end) stash(nt_next, bufs + (which ^ 1) * buf_floats);
     __syncthreads();
@@ -787,7 +794,8 @@ int matrix_recurrence_launch(int mode, const T* q, int64_t q_stride, const T* k,
   const size_t smem = sizeof(float) * 2 * (size_t)tc * (2 * dkp + cols + 4);
   void (*kernel)(int, const T*, int64_t, const T*, int64_t, const T*, int64_t, const float*, int64_t, const float*,
                  const float*, float, float*, const int*, const int*, float*, int64_t, int, int, int, int, int);
-  kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS> : matrix_recurrence_kernel<T, 16, REC_THREADS>;
+  if (mode == 1) kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS, 1> : matrix_recurrence_kernel<T, 16, REC_THREADS, 1>;
+  else kernel = dpt == 4 ? matrix_recurrence_kernel<T, 4, REC_THREADS, 0> : matrix_recurrence_kernel<T, 16, REC_THREADS, 0>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
