@@ -500,6 +500,7 @@ DESIGN_SIZES = {
 
 
 def guvetar_raw(sz: dict) -> dict:
+    """Two layers of each mixer kind in turn (the shipped presets ``guvetar-w2048`` / ``guvetar-w1024`` are these)."""
     mamba = {"type": "mamba1", "mixer": {"inner": sz["inner"], "state": sz["state"], "dt_rank": sz["dt_rank"], "conv": 4}}
     memory = {"type": "mlstm", "mixer": {"heads": sz["memory_heads"], "dim": sz["memory_dim"], "vdim": sz["memory_vdim"],
                                          "gate_cap": 15.0}}

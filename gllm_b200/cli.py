@@ -75,7 +75,10 @@ def cmd_make_random(args) -> int:
     else:
         raw = load_preset(args.preset)
     if args.num_layers is not None:
-        raw["num_hidden_layers"] = args.num_layers
+        if isinstance(raw.get("layers"), list):          # a config that lists its layers: keep the first ones
+            raw["layers"] = raw["layers"][: args.num_layers]
+        else:
+            raw["num_hidden_layers"] = args.num_layers
     if args.dtype:
         raw["torch_dtype"] = args.dtype
     write_random_model(args.out, load_config(raw), seed=args.seed, std=args.std, norm_jitter=args.norm_jitter)
