@@ -503,12 +503,12 @@ def guvetar_raw(sz: dict) -> dict:
     """Two layers of each mixer kind in turn (the shipped presets ``guvetar-w2048`` / ``guvetar-w1024`` are these)."""
     mamba = {"type": "mamba1", "mixer": {"inner": sz["inner"], "state": sz["state"], "dt_rank": sz["dt_rank"], "conv": 4}}
     memory = {"type": "mlstm", "mixer": {"heads": sz["memory_heads"], "dim": sz["memory_dim"], "vdim": sz["memory_vdim"],
-                                         "gate_cap": 15.0}}
+                                         "gate_cap": 12.0}}
     pair = {"type": "parallel", "mixer": {
         "left": {"heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["head_dim"], "vdim": sz["head_dim"],
-                 "scale": sz["head_dim"] ** -0.5, "q_temp": {"coef": 0.5, "every": 64}},
+                 "scale": sz["head_dim"] ** -0.5, "q_temp": {"coef": 0.25, "every": 128}},
         "right": {"heads": sz["linear_heads"], "dim": sz["linear_dim"], "vdim": sz["linear_vdim"]},
-        "left_scale": 0.5, "right_scale": 0.5}}
+        "left_scale": 0.7, "right_scale": 0.6}}
     kinds = [mamba, memory, pair]
     layers = [{**kinds[i % 3], "mlp": {"kind": "dense", "ff": sz["ff"]}} for i in range(sz["layers"])]
     return {"architecture": "Guvetar", "vocab": sz["vocab"], "width": sz["width"], "streams": 4, "norm": {"eps": 1e-5},

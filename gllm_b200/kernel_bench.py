@@ -294,7 +294,7 @@ def matrix_recurrence(tokens=2048, batch=1, heads=16, dk=64, dv=128, mode=0, ite
     mstate = torch.zeros(batch + 1, heads, device="cuda")
     b = _Batch(batch, tokens, 0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = lambda: stateful.matrix_recurrence(mode, q, k if mode else None, v, gates, gbias, None if mode else lower, 15.0,
+    fn = lambda: stateful.matrix_recurrence(mode, q, k if mode else None, v, gates, gbias, None if mode else lower, 12.0,
                                             dk ** -0.5, state, mstate if mode else None, b.cu_q, b.state_slots, batch,
                                             heads, dk, dv, max_q_len=tokens)
     us = _time(fn, iters, flush)

@@ -66,8 +66,8 @@ GUVETAR_C = {
         _layer(_mamba(128, 40, 16, 1), 64),
         _layer(_parallel({"heads": 4, "kv_heads": 1, "dim": 40, "vdim": 72, "scale": 0.16,
                           "q_temp": {"coef": 0.25, "every": 16}},
-                         {"heads": 3, "dim": 40, "vdim": 8}, 0.5, 0.5), 128),
-        _layer(_mlstm(1, 64, 40, 15.0), 72),
+                         {"heads": 3, "dim": 40, "vdim": 8}, 0.6, 0.45), 128),
+        _layer(_mlstm(1, 64, 40, 9.0), 72),
     ],
 }
 # no attention at all (no cache pages, only states), four streams
@@ -99,7 +99,7 @@ def single_mixer(kind: str, streams=None) -> dict:
         "mamba1": _mamba(40, 6, 5, 4),
         "mlstm": _mlstm(2, 12, 20, 12.0),
         "parallel": _parallel({"heads": 2, "kv_heads": 1, "dim": 12, "vdim": 20, "scale": 0.4,
-                               "q_temp": {"coef": 0.5, "every": 3}}, {"heads": 2, "dim": 6, "vdim": 10}, 0.9, 0.6),
+                               "q_temp": {"coef": 0.4, "every": 3}}, {"heads": 2, "dim": 6, "vdim": 10}, 0.9, 0.6),
         "sigmoid_only": _parallel({"heads": 2, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.35},
                                   {"heads": 1, "dim": 4, "vdim": 4}, 1.0, 0.0),
         "hgrn2_only": _parallel({"heads": 1, "kv_heads": 1, "dim": 8, "vdim": 8, "scale": 0.3},
