@@ -83,8 +83,8 @@ class GuvetarConfig(ModelConfig):
         if dtype not in DTYPE_NAMES:
             raise ConfigError(f"unsupported dtype {dtype!r}")
         streams = d.get("streams")
-        if streams is not None and not 1 <= int(streams) <= 8:
-            raise ConfigError("'streams' must be between 1 and 8")
+        if streams is not None and not 1 <= int(streams) <= 16:
+            raise ConfigError("'streams' must be between 1 and 16")
         vocab, width = int(require(d, "vocab")), int(require(d, "width"))
         if vocab <= 0 or width <= 0:
             raise ConfigError("'vocab' and 'width' must be positive")

@@ -10,7 +10,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int MAX_STREAMS = 8;
+constexpr int MAX_STREAMS = 16;
 
 // Token embedding (+ a sinusoid of the position: column 2i = sin(p f_i), 2i+1 = cos(p f_i), with the
 // frequencies f_i given in fp32 and the angle formed in fp32), copied into every stream.  A negative
@@ -67,7 +67,7 @@ stream_mix_norm_kernel(const T* __restrict__ y, float* __restrict__ X, const flo
   float ss = 0.f;
   // four columns a thread at a time: all their loads are asked for before the first store (the streams are
   // read and written through the same pointer, so the compiler keeps loads behind earlier stores)
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = STREAMS > 8 ? 1 : 4;
   for (int c0 = threadIdx.x; c0 < width; c0 += UNROLL * blockDim.x) {
     float old[UNROLL][STREAMS], yv[UNROLL];
 #pragma unroll
@@ -143,7 +143,15 @@ int stream_mix_norm_launch(const T* y, float* X, const float* mix, const float* 
     case 5: kernel = stream_mix_norm_kernel<T, 5>; break;
     case 6: kernel = stream_mix_norm_kernel<T, 6>; break;
     case 7: kernel = stream_mix_norm_kernel<T, 7>; break;
-    default: kernel = stream_mix_norm_kernel<T, 8>; break;
+    case 8: kernel = stream_mix_norm_kernel<T, 8>; break;
+    case 9: kernel = stream_mix_norm_kernel<T, 9>; break;
+    case 10: kernel = stream_mix_norm_kernel<T, 10>; break;
+    case 11: kernel = stream_mix_norm_kernel<T, 11>; break;
+    case 12: kernel = stream_mix_norm_kernel<T, 12>; break;
+    case 13: kernel = stream_mix_norm_kernel<T, 13>; break;
+    case 14: kernel = stream_mix_norm_kernel<T, 14>; break;
+    case 15: kernel = stream_mix_norm_kernel<T, 15>; break;
+    default: kernel = stream_mix_norm_kernel<T, 16>; break;
   }
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -17,7 +17,7 @@ def close(got, want, tol):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("streams,width", [(1, 40), (3, 72), (4, 256), (8, 100)])
+@pytest.mark.parametrize("streams,width", [(1, 40), (3, 72), (4, 256), (8, 100), (16, 64)])
 def test_embed_streams(dtype, streams, width):
     from gllm_b200.ops import stateful
 
@@ -37,7 +37,7 @@ def test_embed_streams(dtype, streams, width):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("streams,width", [(1, 48), (2, 64), (4, 200), (7, 96), (8, 1024)])
+@pytest.mark.parametrize("streams,width", [(1, 48), (2, 64), (4, 200), (7, 96), (8, 1024), (11, 72), (16, 128)])
 def test_stream_mix_norm(dtype, streams, width):
     from gllm_b200.ops import stateful
 
