@@ -98,9 +98,9 @@ attention_sigmoid_kernel(const T* __restrict__ q, int64_t q_stride, T* __restric
   const float bias = head_bias ? head_bias[h] : 0.f;
   const size_t page_elems = (size_t)hkv * block_size * (dk + dv);
   const size_t v_base = (size_t)hkv * block_size * dk;
-  float acc[MAX_DV / 32];
+  float acc[MAX_DV / 32], lost[MAX_DV / 32];
 #pragma unroll
-  for (int i = 0; i < MAX_DV / 32; ++i) acc[i] = 0.f;
+  for (int i = 0; i < MAX_DV / 32; ++i) acc[i] = lost[i] = 0.f;
   for (int j0 = 0; j0 <= qpos; j0 += 32) {
     const int j = j0 + lane;
     float p = 0.f;
@@ -118,8 +118,9 @@ attention_sigmoid_kernel(const T* __restrict__ q, int64_t q_stride, T* __restric
         vbase = (int64_t)((size_t)page * page_elems + v_base + ((size_t)kvh * block_size + off) * dv);
       }
     }
-    // the block's 32 terms are added up by themselves and then added to the total: the rounding error of a
-    // long context grows with the number of blocks, not with the number of keys
+    // the block's 32 terms are added up by themselves and then added to the total with the low-order bits that
+    // the addition drops carried along (compensated summation): the rounding error of a long context stays that
+    // of one block
     float part[MAX_DV / 32];
 #pragma unroll
     for (int i = 0; i < MAX_DV / 32; ++i) part[i] = 0.f;
@@ -136,7 +137,12 @@ attention_sigmoid_kernel(const T* __restrict__ q, int64_t q_stride, T* __restric
       }
     }
 #pragma unroll
-    for (int i = 0; i < MAX_DV / 32; ++i) acc[i] += part[i];
+    for (int i = 0; i < MAX_DV / 32; ++i) {
+      const float y = part[i] - lost[i];
+      const float t = acc[i] + y;
+      lost[i] = (t - acc[i]) - y;
+      acc[i] = t;
+    }
   }
   T* o = out + (int64_t)n * out_stride + (int64_t)h * dv;
 #pragma unroll
