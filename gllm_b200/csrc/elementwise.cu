@@ -899,6 +899,194 @@ GLLM_API int gllm_rope_store_bf16(__nv_bfloat16* qkv, const float* parts, int n_
                                           num_pages, status, stream);
 }
 
+// ------------------------------------------- gated activation with clamped inputs
+// gate_up is [n, 2*inter] laid out as for silu_mul (block == 0: gate columns first; block > 0: blocks of
+// `block` gate columns alternate with the up columns of the same features).
+//   g = min(gate, limit), u = clamp(up, -limit, limit)           (limit <= 0: no clamps)
+//   out = g * sigmoid(slope * g) * (u + up_offset)
+// slope 1, no limit and offset 0 is silu(gate) * up.  Computed in fp32.
+__device__ __forceinline__ float gated_act_value(float g, float u, float slope, float limit, float up_offset) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  return g / (1.0f + expf(-slope * g)) * (u + up_offset);
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter, int block,
+                                 float slope, float limit, float up_offset) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t total = (size_t)n_rows * inter;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / inter, c = idx - r * inter;
+    const size_t gc = block ? (c / block) * 2 * block + c % block : c;
+    const float g = to_float(gate_up[r * 2 * inter + gc]);
+    const float u = to_float(gate_up[r * 2 * inter + gc + (block ? block : inter)]);
+    out[idx] = from_float<T>(gated_act_value(g, u, slope, limit, up_offset));
+  }
+}
+
+template <typename T>
+__global__ void gated_act_wide_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
+                                      int block, float slope, float limit, float up_offset) {
+  pdl_trigger();
+  pdl_wait();
+  const int per_row = inter / 8;
+  const size_t total = (size_t)n_rows * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / per_row;
+    const int c = (int)(idx - r * per_row) * 8;
+    float g[8], u[8], y[8];
+    const int gc = block ? (c / block) * 2 * block + c % block : c;
+    Vec8<T>::load(gate_up + r * 2 * inter + gc, g);
+    Vec8<T>::load(gate_up + r * 2 * inter + gc + (block ? block : inter), u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = gated_act_value(g[e], u[e], slope, limit, up_offset);
+    Vec8<T>::store(out + r * inter + c, y);
+  }
+}
+
+template <typename T>
+static int gated_act_launch(const T* gate_up, T* out, int n_rows, int inter, int block, float slope, float limit,
+                            float up_offset, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (block < 0 || (block > 0 && inter % block)) return (int)cudaErrorInvalidValue;
+  if (inter % 8 == 0 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+    const size_t chunks = (size_t)n_rows * (inter / 8);
+    int wide_blocks = (int)((chunks + 255) / 256);
+    if (wide_blocks > gllm_sm_count() * 16) wide_blocks = gllm_sm_count() * 16;
+    return gllm_launch(gated_act_wide_kernel<T>, dim3(wide_blocks), dim3(256), 0, stream, gate_up, out, n_rows,
+                       inter, block, slope, limit, up_offset);
+  }
+  const size_t total = (size_t)n_rows * inter;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > gllm_sm_count() * 16) blocks = gllm_sm_count() * 16;
+  return gllm_launch(gated_act_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter, block,
+                     slope, limit, up_offset);
+}
+GLLM_API int gllm_gated_act_f32(const float* gate_up, float* out, int n_rows, int inter, int block, float slope,
+                                float limit, float up_offset, cudaStream_t stream) {
+  return gated_act_launch<float>(gate_up, out, n_rows, inter, block, slope, limit, up_offset, stream);
+}
+GLLM_API int gllm_gated_act_bf16(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int n_rows, int inter, int block,
+                                 float slope, float limit, float up_offset, cudaStream_t stream) {
+  return gated_act_launch<__nv_bfloat16>(gate_up, out, n_rows, inter, block, slope, limit, up_offset, stream);
+}
+
+// ------------------------------------------- a branch added into the residual; the residual joined with another
+// residual_add: resid[r, c] += branch[r, c] (fp32 sum; the branch is a tensor of T or `n_parts` unsummed fp32
+// splits, which are summed in ascending order and rounded to T first, as the product would have rounded them).
+// For a layer whose two branches read one norm: the first branch is added at once, the second by the next norm.
+// join_rows: out[r] = [ resid[r] (+ branch[r]) ; other[r] ] as T, `hidden` columns each: the input of a product
+// over the residual and a second fp32 stream of the same width.  resid is not written.
+template <typename T, bool JOIN>
+__global__ void __launch_bounds__(256)
+residual_add_kernel(const T* __restrict__ branch, const float* __restrict__ parts, int n_parts, int64_t part_stride,
+                    float* __restrict__ resid, const float* __restrict__ other, T* __restrict__ out, int64_t total,
+                    int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  float x = resid[i];
+  if (parts) x += to_float(from_float<T>(sum_parts16(parts + i, n_parts, part_stride)));
+  else if (branch) x += to_float(branch[i]);
+  if (JOIN) {
+    const int64_t r = i / hidden, c = i - r * hidden;
+    out[r * 2 * hidden + c] = from_float<T>(x);
+    out[r * 2 * hidden + hidden + c] = from_float<T>(other[i]);
+  } else {
+    resid[i] = x;
+  }
+}
+#define GLLM_RESIDUAL_EXPORTS(T, S)                                                                              \
+  GLLM_API int gllm_residual_add_##S(const T* branch, const float* parts, int n_parts, int64_t part_stride,     \
+                                     float* resid, int64_t total, cudaStream_t stream) {                        \
+    if (total <= 0) return 0;                                                                                    \
+    if (n_parts > 16) return (int)cudaErrorInvalidValue;                                                         \
+    return gllm_launch(residual_add_kernel<T, false>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,       \
+                       stream, branch, parts, n_parts, part_stride, resid, (const float*)nullptr, (T*)nullptr,   \
+                       total, 1);                                                                                \
+  }                                                                                                              \
+  GLLM_API int gllm_join_rows_##S(const T* branch, const float* parts, int n_parts, int64_t part_stride,        \
+                                  float* resid, const float* other, T* out, int64_t rows, int hidden,           \
+                                  cudaStream_t stream) {                                                         \
+    if (rows <= 0) return 0;                                                                                     \
+    if (n_parts > 16 || hidden <= 0) return (int)cudaErrorInvalidValue;                                          \
+    const int64_t total = rows * hidden;                                                                         \
+    return gllm_launch(residual_add_kernel<T, true>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,        \
+                       stream, branch, parts, n_parts, part_stride, resid, other, out, total, hidden);          \
+  }
+GLLM_RESIDUAL_EXPORTS(float, f32)
+GLLM_RESIDUAL_EXPORTS(__nv_bfloat16, bf16)
+
+// ------------------------------------------- RMS norm of whole query and key projections; values = raw keys
+// src is [n, (hq + hkv) * d]: the q projection, then the k projection (a tensor of T, or `n_parts` unsummed fp32
+// splits of the product, summed in ascending order and rounded to T first).  dst is [n, (hq + 2 * hkv) * d]:
+//   q' = q / sqrt(mean(q^2) + eps) * wq    over ALL hq * d columns of the projection at once (wq: hq * d weights)
+//   k' = k / sqrt(mean(k^2) + eps) * wk    over all hkv * d columns
+//   v  = k as projected (with `values_from_keys`; otherwise src has a v projection after k, which is copied)
+// wq / wk null: that projection is copied un-normed.  Statistics in fp32.  One block per token.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_rownorm_kernel(const T* __restrict__ src, int64_t src_stride, const float* __restrict__ parts, int n_parts,
+                  int64_t part_stride, const float* __restrict__ wq, const float* __restrict__ wk,
+                  T* __restrict__ dst, int n_tokens, int q_cols, int k_cols, int values_from_keys, float eps) {
+  extern __shared__ float qk_row[];  // q_cols + k_cols floats + 32 scratch
+  float* scratch = qk_row + q_cols + k_cols;
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  const int in_cols = q_cols + k_cols + (values_from_keys ? 0 : k_cols);
+  float sq = 0.f, sk = 0.f;
+  for (int c = threadIdx.x; c < q_cols + k_cols; c += blockDim.x) {
+    float x;
+    if (parts) x = to_float(from_float<T>(sum_parts16(parts + (size_t)n * in_cols + c, n_parts, part_stride)));
+    else x = to_float(src[(size_t)n * src_stride + c]);
+    qk_row[c] = x;
+    if (c < q_cols) sq += x * x; else sk += x * x;
+  }
+  const float tq = block_sum(sq, scratch);
+  const float tk = block_sum(sk, scratch);
+  const float inv_q = 1.0f / sqrtf(tq / (float)q_cols + eps);
+  const float inv_k = 1.0f / sqrtf(tk / (float)k_cols + eps);
+  T* o = dst + (size_t)n * (q_cols + 2 * k_cols);
+  for (int c = threadIdx.x; c < q_cols; c += blockDim.x)
+    o[c] = from_float<T>(wq ? qk_row[c] * inv_q * wq[c] : qk_row[c]);
+  for (int c = threadIdx.x; c < k_cols; c += blockDim.x) {
+    const float x = qk_row[q_cols + c];
+    o[q_cols + c] = from_float<T>(wk ? x * inv_k * wk[c] : x);
+    float v = x;
+    if (!values_from_keys) {
+      const int vc = q_cols + k_cols + c;
+      v = parts ? to_float(from_float<T>(sum_parts16(parts + (size_t)n * in_cols + vc, n_parts, part_stride)))
+                : to_float(src[(size_t)n * src_stride + vc]);
+    }
+    o[q_cols + k_cols + c] = from_float<T>(v);
+  }
+}
+#define GLLM_QK_ROWNORM_EXPORTS(T, S)                                                                            \
+  GLLM_API int gllm_qk_rownorm_##S(const T* src, int64_t src_stride, const float* parts, int n_parts,           \
+                                   int64_t part_stride, const float* wq, const float* wk, T* dst, int n_tokens, \
+                                   int q_cols, int k_cols, int values_from_keys, float eps,                     \
+                                   cudaStream_t stream) {                                                        \
+    if (n_tokens <= 0) return 0;                                                                                 \
+    if (q_cols <= 0 || k_cols <= 0 || n_parts > 16) return (int)cudaErrorInvalidValue;                           \
+    const size_t smem = (size_t)(q_cols + k_cols + 32) * sizeof(float);                                          \
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;                                                    \
+    if (smem > 48 * 1024)                                                                                        \
+      cudaFuncSetAttribute(qk_rownorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+    return gllm_launch(qk_rownorm_kernel<T>, dim3((unsigned)n_tokens), dim3(256), smem, stream, src, src_stride, \
+                       parts, n_parts, part_stride, wq, wk, dst, n_tokens, q_cols, k_cols, values_from_keys, eps); \
+  }
+GLLM_QK_ROWNORM_EXPORTS(float, f32)
+GLLM_QK_ROWNORM_EXPORTS(__nv_bfloat16, bf16)
+
 // ---------------------------------------------------------------- squared ReLU, weighted sum of two branches
 // out = max(x, 0)^2 (the activation of a dense feed-forward without a gate), and out = a * x + b * y
 // (two mixers that run side by side on the same input), both computed in fp32.

@@ -46,6 +46,8 @@ def expected_tensors_of_spec(spec: ModelSpec) -> dict[str, TensorExpectation]:
     for layer_spec in spec.layers:
         for part in _build_layer(layer_spec).parts():
             exp.update(part.expected_tensors())
+    if spec.rejoin_name is not None:
+        exp[spec.rejoin_name] = TensorExpectation((spec.hidden_size, 2 * spec.hidden_size), "matrix")
     exp.update(build_part(NORMS, spec.final_norm).expected_tensors())
     if spec.head_name is not None:
         exp[spec.head_name] = TensorExpectation((spec.vocab_size, spec.hidden_size), "matrix")
@@ -64,6 +66,7 @@ class DecoderModel:
         self.final_norm: Norm = build_part(NORMS, spec.final_norm)
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
+        self.rejoin: torch.Tensor | None = None
         self._frequencies: torch.Tensor | None = None
 
     @property
@@ -80,6 +83,8 @@ class DecoderModel:
         for block in self.layers:
             for part in block.parts():
                 exp.update(part.expected_tensors())
+        if self.spec.rejoin_name is not None:
+            exp[self.spec.rejoin_name] = TensorExpectation((self.spec.hidden_size, 2 * self.spec.hidden_size), "matrix")
         exp.update(self.final_norm.expected_tensors())
         if self.spec.head_name is not None:
             exp[self.spec.head_name] = TensorExpectation((self.spec.vocab_size, self.spec.hidden_size), "matrix")
@@ -92,6 +97,8 @@ class DecoderModel:
         for block in self.layers:
             for part in block.parts():
                 part.load(get, self.dtype, self.device)
+        if self.spec.rejoin_name is not None:
+            self.rejoin = get(self.spec.rejoin_name, "matrix").contiguous()
         self.final_norm.load(get, self.dtype, self.device)
         self.head = self.embedding if self.spec.head_name is None else get(self.spec.head_name, "matrix")
         self._sinusoid_frequencies()
@@ -149,7 +156,15 @@ class DecoderModel:
         else:
             resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row, scale=scale)
         branch = None
+        first = None
+        if any(entry.rejoins_embedding for entry in self.spec.plan):
+            # the embedding output is kept: the residual itself is updated in place by the layers
+            first = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row, scale=scale)
         for entry_idx, entry in enumerate(self.spec.plan):
+            if entry.rejoins_embedding:
+                joined = ops.join_rows(None if branch is ops.ADDED else branch, resid, first, self.dtype)
+                resid = ops.linear(joined, self.rejoin, out_dtype=torch.float32)
+                branch = None
             branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)

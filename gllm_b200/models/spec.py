@@ -59,6 +59,10 @@ class PlanEntry:
 
     layer: int
     reads_cache_of: int | None = None
+    # True: before this entry runs, the residual is replaced by ``W [x ; x0]`` with ``x`` the residual as it
+    # stands, ``x0`` the embedding output and ``W`` the model's ``rejoin_name`` tensor ``[hidden, 2 * hidden]``
+    # (a stretch of layers that is run several times re-reads the embedding at the start of each pass).
+    rejoins_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -85,6 +89,9 @@ class ModelSpec:
     # The residual is kept as this many parallel streams ``[tokens, streams * hidden]``, all equal to the
     # embedding at the start; the layers' norms say how sublayers read and write them.
     residual_streams: int = 1
+    # Checkpoint name of the ``[hidden, 2 * hidden]`` matrix of the plan entries that rejoin the embedding
+    # (``PlanEntry.rejoins_embedding``); None when no entry does.
+    rejoin_name: str | None = None
     # Tensor names that a checkpoint may hold and the model does not read
     # (for instance a stored head beside tied embeddings).
     ignorable_names: tuple[str, ...] = ()
@@ -93,6 +100,10 @@ class ModelSpec:
         for i, entry in enumerate(self.plan):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"plan entry {i} names layer {entry.layer}, the model has {len(self.layers)}")
+            if entry.rejoins_embedding and self.rejoin_name is None:
+                raise ValueError(f"plan entry {i} rejoins the embedding, but the model names no matrix for that")
+            if entry.rejoins_embedding and self.residual_streams != 1:
+                raise ValueError("rejoining the embedding is defined for a single residual stream")
             if entry.reads_cache_of is not None:
                 j = entry.reads_cache_of
                 if not 0 <= j < i:

@@ -43,6 +43,10 @@ __all__ = [
     "rmsnorm_heads",
     "relu_sq",
     "scaled_sum",
+    "gated_activation",
+    "residual_add",
+    "join_rows",
+    "qk_rownorm",
 ]
 
 P = c_void_p
@@ -58,6 +62,10 @@ _SIGNATURES = {
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
         "gllm_relu_sq_{t}": [P, P, c_int64, P],
         "gllm_scaled_sum_{t}": [P, P, P, c_float, c_float, c_int64, P],
+        "gllm_gated_act_{t}": [P, P, c_int, c_int, c_int, c_float, c_float, c_float, P],
+        "gllm_residual_add_{t}": [P, P, c_int, c_int64, P, c_int64, P],
+        "gllm_join_rows_{t}": [P, P, c_int, c_int64, P, P, P, c_int64, c_int, P],
+        "gllm_qk_rownorm_{t}": [P, c_int64, P, c_int, c_int64, P, P, P, c_int, c_int, c_int, c_int, c_float, P],
         "gllm_rope_store_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, P, P],
     },
@@ -86,6 +94,13 @@ _SIGNATURES = {
                                    c_int, c_int, c_int, P, P],
         "gllm_attention_sigmoid_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_float, P, P],
+    },
+    "attention_latent": {
+        "gllm_latent_prep_{t}": [P, c_int64, P, c_float, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, P, P],
+        "gllm_head_linear_{t}": [P, c_int64, c_int, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, P],
+        "gllm_attention_latent_{t}": [P, c_int64, c_int, P, c_int64, c_int, P, c_int64, P, c_int64, c_int, P, P, c_int,
+                                      P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P],
     },
     "attention_simt": {
         "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
@@ -453,19 +468,25 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = GATED_
     return stacked.reshape(2 * inter, hidden).contiguous()
 
 
-def linear_gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """``silu(x @ Wg.T) * (x @ Wu.T)`` for a weight stacked by ``interleave_gate_up``: one kernel
-    with the activation in the product's epilogue where the tensor-core kernel takes the operands,
-    the product and ``silu_mul`` otherwise."""
+def linear_gated(x: torch.Tensor, weight: torch.Tensor, slope: float = 1.0, limit: float | None = None,
+                 up_offset: float = 0.0) -> torch.Tensor:
+    """``a(x @ Wg.T) * (x @ Wu.T + up_offset)`` for a weight stacked by ``interleave_gate_up``, with
+    ``a(g) = g * sigmoid(slope * g)`` and, with ``limit``, the gate capped at ``limit`` and the up product
+    clamped to ``[-limit, limit]`` first (the defaults are ``silu(gate) * up``): one kernel with the activation
+    in the product's epilogue where the tensor-core kernel takes the operands, the product and the pointwise
+    kernel otherwise."""
     _cuda(x, "x")
     _cuda(weight, "weight", x.dtype)
+    plain = slope == 1.0 and limit is None and up_offset == 0.0
     if x.dtype == torch.bfloat16:
         from gllm_b200.ops import gemm_bf16
 
-        fused = gemm_bf16.linear_gated(x, weight)
+        fused = gemm_bf16.linear_gated(x, weight, slope=slope, limit=limit, up_offset=up_offset)
         if fused is not None:
             return fused
-    return silu_mul(linear(x, weight), block=GATED_BLOCK)
+    if plain:
+        return silu_mul(linear(x, weight), block=GATED_BLOCK)
+    return gated_activation(linear(x, weight), slope=slope, limit=limit, up_offset=up_offset, block=GATED_BLOCK)
 
 
 def relu_sq(x: torch.Tensor) -> torch.Tensor:
@@ -486,6 +507,97 @@ def scaled_sum(x: torch.Tensor, y: torch.Tensor, a: float, b: float) -> torch.Te
     out = torch.empty_like(x)
     f = _fn("elementwise", f"gllm_scaled_sum_{_suffix(x.dtype)}")
     _check(f(x.data_ptr(), y.data_ptr(), out.data_ptr(), float(a), float(b), x.numel(), _stream()), "scaled_sum")
+    return out
+
+
+# ------------------------------- gated activation with clamps; residual add; join; whole-projection norm
+def gated_activation(gate_up: torch.Tensor, slope: float = 1.0, limit: float | None = None, up_offset: float = 0.0,
+                     block: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``g * sigmoid(slope * g) * (u + up_offset)`` of ``[n, 2*inter]`` with ``g = min(gate, limit)`` and
+    ``u = clamp(up, -limit, limit)`` (no clamps without ``limit``); columns laid out as for ``silu_mul``."""
+    _cuda(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise ValueError("gate_up must have an even number of columns")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("elementwise", f"gllm_gated_act_{_suffix(gate_up.dtype)}")
+    _check(f(gate_up.data_ptr(), out.data_ptr(), n, inter, int(block), float(slope), float(limit or 0.0),
+             float(up_offset), _stream()), "gated_activation")
+    return out
+
+
+def residual_add(resid: torch.Tensor, branch, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``resid += branch`` in place on the fp32 residual stream; ``branch`` is a tensor of the activation type
+    or a SplitSum (summed in ascending order and rounded to its type first)."""
+    _cuda(resid, "resid", torch.float32)
+    parts_ptr, n_parts, part_stride = _parts_args(branch)
+    if isinstance(branch, SplitSum):
+        if tuple(branch.shape) != tuple(resid.shape):
+            raise ValueError("branch and resid differ in shape")
+        t, ptr = branch.dtype, None
+    else:
+        _cuda(branch, "branch")
+        if branch.shape != resid.shape:
+            raise ValueError("branch and resid differ in shape")
+        t, ptr = branch.dtype, branch.data_ptr()
+    f = _fn("elementwise", f"gllm_residual_add_{_suffix(t)}")
+    _check(f(ptr, parts_ptr, n_parts, part_stride, resid.data_ptr(), resid.numel(), _stream()), "residual_add")
+    return resid
+
+
+def join_rows(branch, resid: torch.Tensor, other: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``[resid (+ branch) ; other]`` as ``[n, 2 * hidden]`` of ``out_dtype``: the residual stream (with a branch
+    that has not been added yet: a tensor, a SplitSum or None) beside a second fp32 stream of the same shape."""
+    _cuda(resid, "resid", torch.float32)
+    _cuda(other, "other", torch.float32)
+    if other.shape != resid.shape or resid.dim() != 2:
+        raise ValueError("join_rows takes two [n, hidden] streams of equal shape")
+    parts_ptr, n_parts, part_stride = _parts_args(branch)
+    ptr = None
+    if isinstance(branch, SplitSum):
+        if tuple(branch.shape) != tuple(resid.shape) or branch.dtype != out_dtype:
+            raise ValueError("branch and resid differ in shape or dtype")
+    elif branch is not None:
+        _cuda(branch, "branch", out_dtype)
+        if branch.shape != resid.shape:
+            raise ValueError("branch and resid differ in shape")
+        ptr = branch.data_ptr()
+    n, hidden = resid.shape
+    out = torch.empty((n, 2 * hidden), dtype=out_dtype, device=resid.device)
+    f = _fn("elementwise", f"gllm_join_rows_{_suffix(out_dtype)}")
+    _check(f(ptr, parts_ptr, n_parts, part_stride, resid.data_ptr(), other.data_ptr(), out.data_ptr(), n, hidden,
+             _stream()), "join_rows")
+    return out
+
+
+def qk_rownorm(qk, q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, q_cols: int, k_cols: int,
+               values_from_keys: bool = True) -> torch.Tensor:
+    """From the q and k projections ``[n, q_cols + k_cols]`` (a tensor or a SplitSum; with
+    ``values_from_keys=False`` a v projection of ``k_cols`` follows) to ``[n, q_cols + 2 * k_cols]``: q and k
+    RMS-normed over their WHOLE projection (all heads at once) with one weight per column, values = the keys as
+    projected (or the v projection, copied).  A weight of None leaves that projection un-normed."""
+    parts_ptr, n_parts, part_stride = _parts_args(qk)
+    in_cols = q_cols + k_cols + (0 if values_from_keys else k_cols)
+    if isinstance(qk, SplitSum):
+        n, cols, t, ptr, stride, device = qk.shape[0], qk.shape[1], qk.dtype, None, 0, qk.device
+    else:
+        _cuda(qk, "qk", contiguous=False)
+        if qk.dim() != 2 or qk.stride(1) != 1:
+            raise ValueError("qk must be [tokens, columns] with contiguous columns")
+        n, cols, t, ptr, stride, device = qk.shape[0], qk.shape[1], qk.dtype, qk.data_ptr(), qk.stride(0), qk.device
+    if cols != in_cols:
+        raise ValueError(f"the projection has {cols} columns, {in_cols} were expected")
+    for w, size, name in ((q_weight, q_cols, "q_weight"), (k_weight, k_cols, "k_weight")):
+        if w is not None:
+            _cuda(w, name, torch.float32)
+            if w.numel() != size:
+                raise ValueError(f"{name} needs one value per column of its projection")
+    out = torch.empty((n, q_cols + 2 * k_cols), dtype=t, device=device)
+    f = _fn("elementwise", f"gllm_qk_rownorm_{_suffix(t)}")
+    _check(f(ptr, stride, parts_ptr, n_parts, part_stride, _ptr(q_weight), _ptr(k_weight), out.data_ptr(), n,
+             int(q_cols), int(k_cols), int(values_from_keys), float(eps), _stream()), "qk_rownorm")
     return out
 
 

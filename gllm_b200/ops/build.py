@@ -52,6 +52,7 @@ MODULES = {
     "hyper_streams": "hyper_streams.cu",
     "attention_sigmoid": "attention_sigmoid.cu",
     "attention_sigmoid_mma": "attention_sigmoid_mma.cu",
+    "attention_latent": "attention_latent.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -207,10 +207,15 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> tor
     return out
 
 
-def linear_gated(x: torch.Tensor, weight: torch.Tensor):
+def linear_gated(x: torch.Tensor, weight: torch.Tensor, slope: float = 1.0, limit: float | None = None,
+                 up_offset: float = 0.0):
     """``silu(gate) * up`` of a weight stacked in blocks of 64 gate / 64 up rows, fused into the
-    product's epilogue; None when the kernel does not take these operands."""
+    product's epilogue; None when the kernel does not take these operands (or another activation
+    than the plain one is asked for)."""
     from gllm_b200 import ops
+
+    if slope != 1.0 or limit is not None or up_offset != 0.0:
+        return None
 
     n, k = weight.shape
     if not tensor_core_kernel_takes(x, weight) or n % 128:

@@ -1,0 +1,88 @@
+"""Python entry points of ``csrc/attention_latent.cu``: attention over one cached latent vector per
+token.  As everywhere in ``gllm_b200.ops``: CUDA tensors only, no CPU path."""
+
+from __future__ import annotations
+
+import torch
+
+from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix, status_word
+
+
+def _rows(t: torch.Tensor, name: str, dtype=None) -> None:
+    _cuda(t, name, dtype, contiguous=False)
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be [tokens, columns] with contiguous columns")
+
+
+def latent_prep(rows: torch.Tensor, norm_weight: torch.Tensor, eps: float, positions: torch.Tensor,
+                inv_freq: torch.Tensor, slot_mapping: torch.Tensor | None, pages: torch.Tensor, heads: int,
+                q_plain: int, rot: int, rank: int, down_col: int, block_size: int) -> None:
+    """On the projection rows ``[n, >= heads * (q_plain + rot) + rank + rot]``: rotate the last ``rot`` columns
+    of every query head in place (neighbouring pairs, ``2 * len(inv_freq)`` columns of them), and store
+    ``[rms(down[:rank]) * norm_weight ; rotate(down[rank:])]`` of the down-projection at column ``down_col``
+    into the token's cache slot.  ``pages`` is the pool layer ``[pages, block_size * (rank + rot)]``."""
+    _rows(rows, "rows")
+    _cuda(norm_weight, "norm_weight", torch.float32)
+    _cuda(inv_freq, "inv_freq", torch.float32)
+    _cuda(positions, "positions", torch.int32)
+    _cuda(pages, "pages", rows.dtype, contiguous=False)
+    if norm_weight.numel() != rank:
+        raise ValueError("the latent's norm needs one weight per column")
+    if pages.stride(0) != block_size * (rank + rot):
+        raise ValueError("the cache layer's pages are not block_size * (rank + rot) wide")
+    if down_col + rank + rot > rows.shape[1] or heads * (q_plain + rot) > down_col:
+        raise ValueError("the projection rows are narrower than the heads and the down-projection need")
+    if slot_mapping is not None:
+        _cuda(slot_mapping, "slot_mapping", torch.int32)
+    f = _fn("attention_latent", f"gllm_latent_prep_{_suffix(rows.dtype)}")
+    _check(f(rows.data_ptr(), rows.stride(0), norm_weight.data_ptr(), float(eps), positions.data_ptr(),
+             inv_freq.data_ptr(), _ptr(slot_mapping), pages.data_ptr(), rows.shape[0], int(heads),
+             int(q_plain + rot), int(q_plain), int(down_col), int(rank), int(rot), 2 * inv_freq.numel(),
+             int(block_size), pages.shape[0], status_word(rows.device).data_ptr(), _stream()), "latent_prep")
+
+
+def head_linear(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[n, h, :] = weight[h] @ x[n, h * x_head : h * x_head + I]`` for ``weight [heads, J, I]``: one small
+    product per head in one launch; ``out`` is ``[n, heads * J]``."""
+    _rows(x, "x")
+    _cuda(weight, "weight", x.dtype)
+    heads, j, i = weight.shape
+    if (heads - 1) * x_head + i > x.shape[1]:
+        raise ValueError("the heads do not lie inside the rows of x")
+    n = x.shape[0]
+    if out is None:
+        out = torch.empty((n, heads * j), dtype=x.dtype, device=x.device)
+    f = _fn("attention_latent", f"gllm_head_linear_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), x.stride(0), int(x_head), weight.data_ptr(), out.data_ptr(), out.stride(0), j, n, heads, i,
+             j, _stream()), "head_linear")
+    return out
+
+
+def attention_latent(qa: torch.Tensor, rows: torch.Tensor, q_head: int, q_plain: int, gate_col: int | None,
+                     pages: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                     heads: int, rank: int, rot: int, block_size: int, scale: float, window: int | None = None,
+                     batch=None) -> torch.Tensor:
+    """Softmax attention of every (token, head) over its request's cached ``[c ; kr]`` vectors: scores
+    ``(qa . c + qr . kr) * scale`` with ``qa [n, heads * rank]`` and ``qr`` the rotated part of every query head
+    inside ``rows``; the result ``[n, heads * rank]`` is the weighted sum of the ``c`` (times
+    ``sigmoid(rows[n, gate_col + h])`` with ``gate_col``)."""
+    _rows(qa, "qa")
+    _rows(rows, "rows", qa.dtype)
+    _cuda(pages, "pages", qa.dtype, contiguous=False)
+    _cuda(block_table, "block_table", torch.int32, contiguous=False)
+    _cuda(positions, "positions", torch.int32)
+    _cuda(token_row, "token_row", torch.int32)
+    n = qa.shape[0]
+    if qa.shape[1] != heads * rank or pages.stride(0) != block_size * (rank + rot):
+        raise ValueError("qa or the cache layer does not match heads, rank and rot")
+    out = torch.empty((n, heads * rank), dtype=qa.dtype, device=qa.device)
+    t = _suffix(qa.dtype)
+    item = qa.element_size()
+    f = _fn("attention_latent", f"gllm_attention_latent_{t}")
+    gate_ptr = None if gate_col is None else rows.data_ptr() + gate_col * item
+    _check(f(qa.data_ptr(), qa.stride(0), rank, rows.data_ptr() + q_plain * item, rows.stride(0), int(q_head),
+             gate_ptr, rows.stride(0), out.data_ptr(), out.stride(0), rank, pages.data_ptr(), block_table.data_ptr(),
+             block_table.stride(0), positions.data_ptr(), token_row.data_ptr(), n, int(heads), int(rank), int(rot),
+             int(block_size), pages.shape[0], float(scale), int(window or 0), status_word(qa.device).data_ptr(),
+             _stream()), "attention_latent")
+    return out

@@ -32,12 +32,17 @@ class Attention(Mixer):
 
     def __init__(self, names, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position=None, window: int | None = None, scale: float | None = None, bias: bool = False,
-                 output_bias: bool = False, qk_norm_eps: float | None = None, qk_norm_unit_offset: bool = False):
+                 output_bias: bool = False, qk_norm_eps: float | None = None, qk_norm_unit_offset: bool = False,
+                 qk_norm_whole: bool = False, values_from_keys: bool = False):
         """``bias``: the q, k and v projections add a bias (tensor names ``q_bias``, ``k_bias``, ``v_bias``);
         ``output_bias``: so does the output projection (``o_bias``).  ``qk_norm_eps``: every head of q and of k
         is RMS-normed over its ``head_dim`` values before the rotation, with one weight each for all query heads
         and all key heads (``q_norm``, ``k_norm``).  Llama has none of the three (the reference's projections
-        have no bias, gllm/model/layers/attention.py:139-142); they are here for architectures that do."""
+        have no bias, gllm/model/layers/attention.py:139-142); they are here for architectures that do.
+        ``qk_norm_whole``: the norm of ``qk_norm_eps`` runs over the WHOLE q projection (all heads at once) and
+        the whole k projection, with one weight per column (``q_norm``: heads * head_dim values).
+        ``values_from_keys``: there is no v projection; the values are the keys as projected, before their norm
+        and rotation."""
         super().__init__(names)
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
@@ -54,6 +59,13 @@ class Attention(Mixer):
         self.bias, self.output_bias = bool(bias), bool(output_bias)
         self.qk_norm_eps = float(qk_norm_eps) if qk_norm_eps is not None else None
         self.qk_norm_unit_offset = bool(qk_norm_unit_offset)
+        self.qk_norm_whole = bool(qk_norm_whole) and self.qk_norm_eps is not None
+        self.values_from_keys = bool(values_from_keys)
+        if (self.qk_norm_whole or self.values_from_keys) and (self.bias or self.qk_norm_unit_offset):
+            raise ValueError("a norm over whole projections and values taken from the keys go without biases and "
+                             "with plain norm weights")
+        if self.values_from_keys and self.qk_norm_eps is not None and not self.qk_norm_whole:
+            raise ValueError("values taken from the keys go with the norm over whole projections (or none)")
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
         self.b_qkv: torch.Tensor | None = None
@@ -72,9 +84,10 @@ class Attention(Mixer):
         exp = {
             self.names["q"]: TensorExpectation((qd, self.hidden_size)),
             self.names["k"]: TensorExpectation((kd, self.hidden_size)),
-            self.names["v"]: TensorExpectation((kd, self.hidden_size)),
-            self.names["o"]: TensorExpectation((self.hidden_size, qd)),
         }
+        if not self.values_from_keys:
+            exp[self.names["v"]] = TensorExpectation((kd, self.hidden_size))
+        exp[self.names["o"]] = TensorExpectation((self.hidden_size, qd))
         if self.bias:
             exp[self.names["q_bias"]] = TensorExpectation((qd,), "bias")
             exp[self.names["k_bias"]] = TensorExpectation((kd,), "bias")
@@ -82,15 +95,15 @@ class Attention(Mixer):
         if self.output_bias:
             exp[self.names["o_bias"]] = TensorExpectation((self.hidden_size,), "bias")
         if self.qk_norm_eps is not None:
-            exp[self.names["q_norm"]] = TensorExpectation((self.head_dim,), "vector")
-            exp[self.names["k_norm"]] = TensorExpectation((self.head_dim,), "vector")
+            exp[self.names["q_norm"]] = TensorExpectation((qd if self.qk_norm_whole else self.head_dim,), "vector")
+            exp[self.names["k_norm"]] = TensorExpectation((kd if self.qk_norm_whole else self.head_dim,), "vector")
         if self.position is not None:
             exp.update(self.position.expected_tensors())
         return exp
 
     def load(self, get, dtype, device):
-        q, k, v = (get(self.names[n], "matrix") for n in ("q", "k", "v"))
-        self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+        projections = ("q", "k") if self.values_from_keys else ("q", "k", "v")
+        self.w_qkv = torch.cat([get(self.names[n], "matrix") for n in projections], dim=0).contiguous()
         self.w_o = get(self.names["o"], "matrix").contiguous()
         if self.bias:
             self.b_qkv = torch.cat([get(self.names[n], "bias") for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
@@ -104,7 +117,11 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache):
         qkv = ops.linear(x, self.w_qkv, split_ok=True, bias=self.b_qkv)
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_whole or self.values_from_keys:
+            qd, kd = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+            qkv = ops.qk_rownorm(qkv, self.w_q_norm, self.w_k_norm, self.qk_norm_eps or 0.0, qd, kd,
+                                 values_from_keys=self.values_from_keys)
+        elif self.qk_norm_eps is not None:
             qkv = ops.as_tensor(qkv)
             ops.rmsnorm_heads(qkv, self.w_q_norm, self.qk_norm_eps, 0, self.num_heads, self.head_dim,
                               self.qk_norm_unit_offset)

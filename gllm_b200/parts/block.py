@@ -30,3 +30,26 @@ class PreNormBlock(Block):
             out = self.feed_forward.forward(x, ctx)
         ctx.residual_sink = None
         return out, resid
+
+
+@register_block("shared_norm")
+class SharedNormBlock(Block):
+    """One norm, two branches that both read its output: ``h = norm(x); x += mixer(h) + feed_forward(h)``.
+    The mixer's result is added into the fp32 residual at once (by its last product where that adds itself,
+    by ``ops.residual_add`` otherwise); the feed-forward's result is handed on un-added, as the pre-norm block
+    does, so that the next norm's kernel adds it.  A layer may have no feed-forward."""
+
+    graph_safe_portions = True
+    part_kinds = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional_parts = frozenset({"feed_forward"})
+
+    def forward(self, branch, resid, ctx, cache):
+        ctx.residual_sink = resid
+        x = self.norm.forward(None if branch is ops.ADDED else branch, resid, ctx.dtype)
+        out = self.mixer.forward(x, ctx, cache)
+        if self.feed_forward is not None:
+            if out is not ops.ADDED:
+                ops.residual_add(resid, out)
+            out = self.feed_forward.forward(x, ctx)
+        ctx.residual_sink = None
+        return out, resid

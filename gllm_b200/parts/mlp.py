@@ -65,6 +65,53 @@ class SwiGLU(FeedForward):
         return ops.linear(hidden, self.w_down, split_ok=True, add_into=sink, bias=self.b_down)
 
 
+@register_feed_forward("clamped_glu")
+class ClampedGLU(FeedForward):
+    """``down(a(g) * (u + up_offset))`` with ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)`` and
+    ``a(g) = g * sigmoid(slope * g)``; the constants are parameters (``limit`` None: no clamps).  Gate and up run
+    as one product; in bfloat16 the activation sits in that product's epilogue when the intermediate size allows
+    the interleaved weight layout, as for ``swiglu``."""
+
+    graph_safe_portions = True
+
+    def __init__(self, names, hidden_size: int, intermediate_size: int, limit: float | None = None,
+                 slope: float = 1.0, up_offset: float = 0.0):
+        super().__init__(names)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit = float(limit) if limit is not None else None
+        if self.limit is not None and not self.limit > 0:
+            raise ValueError("the clamp limit must be positive")
+        self.slope, self.up_offset = float(slope), float(up_offset)
+        self.w_gate_up: torch.Tensor | None = None
+        self.w_down: torch.Tensor | None = None
+        self.gated_blocks = False
+
+    def expected_tensors(self):
+        h, i = self.hidden_size, self.intermediate_size
+        return {
+            self.names["gate"]: TensorExpectation((i, h)),
+            self.names["up"]: TensorExpectation((i, h)),
+            self.names["down"]: TensorExpectation((h, i)),
+        }
+
+    def load(self, get, dtype, device):
+        gate, up = get(self.names["gate"], "matrix"), get(self.names["up"], "matrix")
+        self.gated_blocks = dtype == torch.bfloat16 and self.intermediate_size % ops.GATED_BLOCK == 0
+        if self.gated_blocks:
+            self.w_gate_up = ops.interleave_gate_up(gate, up)
+        else:
+            self.w_gate_up = torch.cat([gate, up], 0).contiguous()
+        self.w_down = get(self.names["down"], "matrix").contiguous()
+
+    def forward(self, x, ctx):
+        act = dict(slope=self.slope, limit=self.limit, up_offset=self.up_offset)
+        if self.gated_blocks:
+            hidden = ops.linear_gated(x, self.w_gate_up, **act)
+        else:
+            hidden = ops.gated_activation(ops.linear(x, self.w_gate_up), **act)
+        return ops.linear(hidden, self.w_down, split_ok=True, add_into=getattr(ctx, "residual_sink", None))
+
+
 @register_feed_forward("dense")
 class DenseFeedForward(FeedForward):
     """``down(act(up(x)))`` without a gate.  ``activation`` "relu_squared": ``max(z, 0) ** 2``."""
