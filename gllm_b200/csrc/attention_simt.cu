@@ -1,5 +1,5 @@
 // Causal attention over the paged cache on the CUDA cores, for any head size
-// that is a multiple of 16 up to 256 and any number of heads and groups.
+// up to 256 and any number of heads and groups.
 // It is the whole attention of the 32-bit path and the fallback of the bf16
 // path for head sizes its tensor-core kernels do not take.
 //
@@ -107,7 +107,7 @@ int attention_simt_launch(const T* q, int64_t q_stride, T* out, int64_t out_stri
                           int n_tokens, int hq, int hkv, int d, int block_size, int num_pages, float scale,
                           int window, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (d <= 0 || d > MAX_D || d % 16 || hq <= 0 || hkv <= 0 || hq % hkv) return (int)cudaErrorInvalidValue;
+  if (d <= 0 || d > MAX_D || hq <= 0 || hkv <= 0 || hq % hkv) return (int)cudaErrorInvalidValue;
   const int64_t items = (int64_t)n_tokens * hq;
   const int64_t blocks = (items + WARPS - 1) / WARPS;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;

@@ -751,8 +751,8 @@ def paged_attention(
     num_pages, two, hkv, block_size, d = cache_layer.shape
     if two != 2:
         raise ValueError("cache layer must be [pages, 2, kv_heads, block_size, head_dim]")
-    if d % 16 or d > 256:
-        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 16 up to 256")
+    if d > 256:
+        raise ValueError(f"head_dim {d} is not supported: the attention kernels take head sizes up to 256")
     if num_heads % hkv:
         raise ValueError("the number of query heads must be a multiple of the number of kv heads")
     n = qkv.shape[0]

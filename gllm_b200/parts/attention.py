@@ -46,8 +46,8 @@ class Attention(Mixer):
         super().__init__(names)
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
-        if head_dim % 16 or head_dim > 256:
-            raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take multiples of 16 up to 256")
+        if head_dim <= 0 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take head sizes up to 256")
         self.hidden_size = int(hidden_size)
         self.num_heads = int(num_heads)
         self.num_kv_heads = int(num_kv_heads)
