@@ -492,10 +492,10 @@ def run_scenario(args) -> dict:
 DESIGN_SIZES = {
     "w2048": dict(width=2048, ff=8192, layers=6, vocab=32000, heads=32, kv_heads=8, head_dim=64, inner=4096, state=16,
                   dt_rank=128, memory_heads=8, memory_dim=128, memory_vdim=256, linear_heads=16, linear_dim=64,
-                  linear_vdim=128),
+                  linear_vdim=128, latent_heads=16, latent_dim=128, latent_rot=64, latent_rank=512),
     "w1024": dict(width=1024, ff=4096, layers=6, vocab=32000, heads=16, kv_heads=4, head_dim=64, inner=2048, state=16,
                   dt_rank=64, memory_heads=4, memory_dim=128, memory_vdim=256, linear_heads=8, linear_dim=64,
-                  linear_vdim=128),
+                  linear_vdim=128, latent_heads=8, latent_dim=128, latent_rot=64, latent_rank=256),
 }
 
 
@@ -513,6 +513,31 @@ def guvetar_raw(sz: dict) -> dict:
     layers = [{**kinds[i % 3], "mlp": {"kind": "dense", "ff": sz["ff"]}} for i in range(sz["layers"])]
     return {"architecture": "Guvetar", "vocab": sz["vocab"], "width": sz["width"], "streams": 4, "norm": {"eps": 1e-5},
             "layers": layers, "torch_dtype": "bfloat16"}
+
+
+def rulunex_raw(sz: dict) -> dict:
+    """Four layers, the middle two run twice: ``layers`` layer runs in all (latent attention everywhere but one
+    windowed layer inside the repeated stretch), so that a Llama of ``layers`` layers does the same number of
+    layer runs (the shipped presets ``rulunex-w2048`` / ``rulunex-w1024`` are these)."""
+    latent = {"type": "latent_attention", "mixer": {
+        "heads": sz["latent_heads"], "dim": sz["latent_dim"], "rot_dim": sz["latent_rot"], "vdim": sz["latent_dim"],
+        "kv_rank": sz["latent_rank"], "scale": (sz["latent_dim"] + sz["latent_rot"]) ** -0.5,
+        "rot": {"base": 10000.0, "dims": sz["latent_rot"]}}}
+    window = {"type": "attention", "mixer": {
+        "heads": sz["heads"], "kv_heads": sz["kv_heads"], "dim": sz["head_dim"], "vdim": sz["head_dim"],
+        "scale": sz["head_dim"] ** -0.5, "mask": {"size": 1024},
+        "rot": {"base": 10000.0, "dims": sz["head_dim"],
+                "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    mlp = {"kind": "dense", "ff": sz["ff"], "limit": 7.0}
+    times = 2
+    inner = (sz["layers"] - 2) // times
+    kinds = [latent] + [window if i == inner - 1 else latent for i in range(inner)] + [latent]
+    return {"architecture": "Rulunex", "vocab": sz["vocab"], "width": sz["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": sz["width"] ** 0.5}, "loop": {"start": 1, "stop": 1 + inner, "times": times},
+            "layers": [{**k, "mlp": mlp} for k in kinds], "torch_dtype": "bfloat16"}
+
+
+DESIGNS = {"guvetar": guvetar_raw, "rulunex": rulunex_raw}
 
 
 def llama_raw(sz: dict) -> dict:
@@ -538,7 +563,7 @@ def run_design(args) -> dict:
         if args.layers:
             sz = dict(sz, layers=args.layers)
         rows[name] = {"sizes": sz}
-        for arm, raw in (("guvetar", guvetar_raw(sz)), ("llama", llama_raw(sz))):
+        for arm, raw in ((args.design, DESIGNS[args.design](sz)), ("llama", llama_raw(sz))):
             tmp = tempfile.mkdtemp(prefix="gllm_b200_bench_")
             try:
                 folder = write_random_model(os.path.join(tmp, arm), load_config(raw), seed=0, std=0.02)
@@ -561,7 +586,7 @@ def run_design(args) -> dict:
             torch.cuda.empty_cache()
     clocks = sampler.stop()
     return {
-        "metric": "prefill (2,048 tokens) and decode (batch 1 and 8, 2,048 cached tokens) throughput of Guvetar beside a "
+        "metric": "prefill (2,048 tokens) and decode (batch 1 and 8, 2,048 cached tokens) throughput of " + args.design.capitalize() + " beside a "
                   "Llama of equal width, feed-forward width, layers and vocabulary (random bf16 weights)",
         "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "higher_is_better": True,
         "data": "synthetic: uniform random token ids, random weights (seed 0)",
@@ -598,7 +623,7 @@ def main() -> int:
     ap.add_argument("--shape", default="", help="with --kernel: overrides such as batch=8,context=2048")
     ap.add_argument("--preset", default=None, choices=sorted(SCENARIOS),
                     help="a whole-engine scenario at another model size (a line of its own, not the headline)")
-    ap.add_argument("--design", default=None, choices=["guvetar"],
+    ap.add_argument("--design", default=None, choices=sorted(DESIGNS),
                     help="another design's prefill and decode throughput beside the closest Llama (a line of its own)")
     args = ap.parse_args()
     if args.kernel:

@@ -1,0 +1,353 @@
+// Latent attention of the bf16 path on the tensor cores: softmax attention of every (token, head) over its
+// request's cached [c ; kr] vectors (RANK + ROT numbers per token, one "key head" for all query heads), the
+// values being the first RANK columns of the keys (see attention_latent.cu for the algebra).
+//
+// One CTA of 8 warps owns 64 rows = (64 / H') tokens x H' heads (H' = all heads when there are at most 64 of
+// them, so that a key tile is fetched once for all heads of a token).  The rows' queries [qa ; qr] stay in
+// shared memory; key tiles of 32 tokens come page by page with cp.async in two stages and serve both products:
+//   S = Q K^T     warp w: rows 16 (w & 3) .., keys 16 (w >> 2) ..           mma.sync m16n8k16, fp32
+//   softmax       four threads per row over the tile's 32 scores (fp32, base 2): running maximum and sum,
+//                 probabilities to shared memory as bf16, the rescaling factor of the row beside them
+//   O = O c + P V warp w: rows 16 (w & 3) .., columns (w >> 2) RANK / 2 ..   V = the tile's first RANK columns
+// Key tiles are aligned to absolute positions, so a token's result does not depend on how its request was cut
+// into steps.  With `splits` > 1 a CTA visits the key tiles [s * tiles_per_split, (s + 1) * tiles_per_split)
+// only and leaves (unnormalised O, maximum, sum) in fp32; latent_merge combines the ranges (single decoded
+// tokens over a long context get enough CTAs that way).  The per-head sigmoid gate multiplies the result.
+#include "mma_utils.cuh"
+
+namespace {
+constexpr int LM_BM = 64, LM_BN = 32, LM_THREADS = 256;
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int C>
+__device__ __forceinline__ int lswz(int row, int piece) {
+  if (C % 8 == 0) return piece ^ (row & 7);
+  return piece ^ ((row >> 1) & 3);
+}
+
+template <int RANK, int ROT>
+__global__ void __launch_bounds__(LM_THREADS)
+latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const __nv_bfloat16* __restrict__ qr,
+                  int64_t qr_stride, int qr_head, const __nv_bfloat16* __restrict__ gate, int64_t gate_stride,
+                  __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ part_o,
+                  float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ cache,
+                  const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
+                  const int* __restrict__ ctx_lens, const int* __restrict__ slots, int n_tokens, int heads, int gp,
+                  int qt, int block_size, int num_pages, float scale_log2, int splits, int tiles_per_split,
+                  int* __restrict__ status) {
+  constexpr int DK = RANK + ROT, CK = DK / 8, CR = RANK / 8, CP = LM_BN / 8;
+  constexpr int Q_BYTES = LM_BM * DK * 2, K_BYTES = LM_BN * DK * 2;
+  constexpr int S_LD = LM_BN + 2;
+  constexpr int NV = RANK / 16;            // n8 tiles of a warp's half of the value columns
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* q_sm = smem_raw;                                   // [64][DK] bf16
+  unsigned char* k_sm0 = q_sm + Q_BYTES;                            // 2 x [32][DK] bf16
+  float* s_sm = reinterpret_cast<float*>(k_sm0 + 2 * K_BYTES);      // [64][S_LD]
+  unsigned char* p_sm = reinterpret_cast<unsigned char*>(s_sm + LM_BM * S_LD);   // [64][32] bf16
+  float* corr_sm = reinterpret_cast<float*>(p_sm + LM_BM * LM_BN * 2);           // [64] rescale, then [64] m, [64] l
+  float* m_sm = corr_sm + LM_BM;
+  float* l_sm = m_sm + LM_BM;
+
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.z;
+  const int h0 = blockIdx.y * gp;
+  const int tok_begin = cu_q[r], q_len = cu_q[r + 1] - tok_begin;
+  const int n_qtiles = (q_len + qt - 1) / qt;
+  const int split = blockIdx.x % splits;
+  const int xt = blockIdx.x / splits;
+  if (xt >= n_qtiles) return;
+  const int qtile = n_qtiles - 1 - xt;                  // longest rows first
+  const int t0 = qtile * qt;
+  const int t_count = min(qt, q_len - t0);
+  const int rows_used = t_count * gp;
+  const int ctx = ctx_lens[r];
+  const int* bt = block_table + (int64_t)slots[r] * bt_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int rb = (warp & 3) * 16, half = warp >> 2;
+
+  const int pos_first = ctx + t0, pos_last = ctx + t0 + t_count - 1;
+  int tile_first = 0, tile_last = pos_last / LM_BN;
+  if (splits > 1) {
+    tile_first = split * tiles_per_split;
+    tile_last = min(tile_last, tile_first + tiles_per_split - 1);
+  }
+
+  // softmax role: thread t owns row t >> 2, keys 8 (t & 3) .. of every tile
+  const int srow = threadIdx.x >> 2, squart = threadIdx.x & 3;
+  const int s_tl = srow / gp;
+  const bool s_ok = srow < rows_used;
+  const int s_qpos = pos_first + s_tl;
+  float m_run = -INFINITY, l_run = 0.f;
+
+  float o[NV][4];
+#pragma unroll
+  for (int nd = 0; nd < NV; ++nd)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nd][e] = 0.f;
+
+  if (tile_first <= tile_last) {
+    for (int idx = threadIdx.x; idx < LM_BM * CK; idx += LM_THREADS) {
+      const int rr = idx / CK, piece = idx - rr * CK;
+      const int tl = rr / gp, g = rr - tl * gp;
+      const bool ok = rr < rows_used;
+      const int64_t token = tok_begin + t0 + (ok ? tl : 0);
+      const __nv_bfloat16* src = piece < CR
+          ? qa + token * qa_stride + (int64_t)(h0 + (ok ? g : 0)) * RANK + piece * 8
+          : qr + token * qr_stride + (int64_t)(h0 + (ok ? g : 0)) * qr_head + (piece - CR) * 8;
+      cp_async16(smem_u32(q_sm + (rr * CK + lswz<CK>(rr, piece)) * 16), src, ok);
+    }
+    auto load_k = [&](int tile, int stage) {
+      unsigned char* dst = k_sm0 + stage * K_BYTES;
+      for (int idx = threadIdx.x; idx < LM_BN * CK; idx += LM_THREADS) {
+        const int row = idx / CK, piece = idx - row * CK;
+        const int key = tile * LM_BN + row;
+        bool ok = key <= pos_last;
+        int page = 0;
+        if (ok) {
+          page = bt[key / block_size];
+          if (page < 0 || page >= num_pages) {
+            atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+            ok = false;
+            page = 0;
+          }
+        }
+        const __nv_bfloat16* src = cache + ((int64_t)page * block_size + key % block_size) * DK + piece * 8;
+        cp_async16(smem_u32(dst + (row * CK + lswz<CK>(row, piece)) * 16), ok ? src : cache, ok);
+      }
+    };
+    load_k(tile_first, 0);
+    cp_async_commit();
+
+    for (int tile = tile_first; tile <= tile_last; ++tile) {
+      const int stage = (tile - tile_first) & 1;
+      if (tile < tile_last) {
+        load_k(tile + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      const unsigned char* k_sm = k_sm0 + stage * K_BYTES;
+      const int kv0 = tile * LM_BN;
+      // ---- S = Q K^T: 16 rows x 16 keys per warp
+      {
+        float s[2][4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+        const int mat = lane >> 3, rl = lane & 7;
+#pragma unroll 4
+        for (int ks = 0; ks < DK / 16; ++ks) {
+          uint32_t a[4], b[4];
+          const int arow = rb + (mat & 1) * 8 + rl;
+          ldmatrix_x4(a, smem_u32(q_sm + (arow * CK + lswz<CK>(arow, 2 * ks + (mat >> 1))) * 16));
+          const int brow = half * 16 + (mat >> 1) * 8 + rl;
+          ldmatrix_x4(b, smem_u32(k_sm + (brow * CK + lswz<CK>(brow, 2 * ks + (mat & 1))) * 16));
+          mma_bf16(s[0], a, b[0], b[1]);
+          mma_bf16(s[1], a, b[2], b[3]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            *reinterpret_cast<float2*>(s_sm + (rb + g8 + 8 * i) * S_LD + half * 16 + nt * 8 + 2 * t4) =
+                make_float2(s[nt][2 * i], s[nt][2 * i + 1]);
+      }
+      __syncthreads();
+      // ---- softmax of the tile: four threads a row
+      {
+        float v[8];
+        float mx = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int key = kv0 + squart * 8 + e;
+          const float x = s_sm[srow * S_LD + squart * 8 + e] * scale_log2;
+          v[e] = (s_ok && key <= s_qpos) ? x : -INFINITY;
+          mx = fmaxf(mx, v[e]);
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        float sum = 0.f;
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 8; e += 2) {
+          const float p0 = (m_new == -INFINITY) ? 0.f : fast_exp2(v[e] - m_new);
+          const float p1 = (m_new == -INFINITY) ? 0.f : fast_exp2(v[e + 1] - m_new);
+          sum += p0 + p1;
+          packed[e >> 1] = pack_bf16(p0, p1);
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const float corr = (m_run == -INFINITY) ? ((m_new == -INFINITY) ? 1.f : 0.f) : fast_exp2(m_run - m_new);
+        l_run = l_run * corr + sum;
+        m_run = m_new;
+        *reinterpret_cast<uint4*>(p_sm + (srow * CP + lswz<CP>(srow, squart)) * 16) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        if (squart == 0) corr_sm[srow] = corr;
+      }
+      __syncthreads();
+      // ---- O = O * corr + P V: 16 rows x RANK / 2 columns per warp
+      {
+        const float c0 = corr_sm[rb + g8], c1 = corr_sm[rb + g8 + 8];
+#pragma unroll
+        for (int nd = 0; nd < NV; ++nd) {
+          o[nd][0] *= c0; o[nd][1] *= c0; o[nd][2] *= c1; o[nd][3] *= c1;
+        }
+        const int mat = lane >> 3, rl = lane & 7;
+#pragma unroll
+        for (int kk = 0; kk < LM_BN / 16; ++kk) {
+          uint32_t a[4];
+          const int arow = rb + (mat & 1) * 8 + rl;
+          ldmatrix_x4(a, smem_u32(p_sm + (arow * CP + lswz<CP>(arow, 2 * kk + (mat >> 1))) * 16));
+#pragma unroll
+          for (int nd2 = 0; nd2 < NV / 2; ++nd2) {
+            const int row = kk * 16 + (mat & 1) * 8 + rl;
+            const int piece = half * (CR / 2) + 2 * nd2 + (mat >> 1);
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, smem_u32(k_sm + (row * CK + lswz<CK>(row, piece)) * 16));
+            mma_bf16(o[2 * nd2], a, b[0], b[1]);
+            mma_bf16(o[2 * nd2 + 1], a, b[2], b[3]);
+          }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  if (squart == 0) {
+    m_sm[srow] = m_run;
+    l_sm[srow] = l_run;
+  }
+  __syncthreads();
+  // ---- store
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = rb + g8 + 8 * i;
+    if (rr >= rows_used) continue;
+    const int tl = rr / gp, g = rr - tl * gp;
+    const int64_t token = tok_begin + t0 + tl;
+    const int head = h0 + g;
+    const int col0 = half * (RANK / 2);
+    if (splits > 1) {
+      float* dst = part_o + (((int64_t)split * n_tokens + token) * heads + head) * RANK + col0;
+#pragma unroll
+      for (int nd = 0; nd < NV; ++nd)
+        *reinterpret_cast<float2*>(dst + nd * 8 + 2 * t4) = make_float2(o[nd][2 * i], o[nd][2 * i + 1]);
+      if (half == 0 && t4 == 0) {
+        float* ml = part_ml + (((int64_t)split * n_tokens + token) * heads + head) * 2;
+        ml[0] = m_sm[rr];
+        ml[1] = l_sm[rr];
+      }
+    } else {
+      const float l = l_sm[rr];
+      float mult = l > 0.f ? 1.0f / l : 0.f;
+      if (gate) mult *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[token * gate_stride + head])));
+      __nv_bfloat16* dst = out + token * out_stride + (int64_t)head * RANK + col0;
+#pragma unroll
+      for (int nd = 0; nd < NV; ++nd)
+        *reinterpret_cast<__nv_bfloat162*>(dst + nd * 8 + 2 * t4) =
+            __floats2bfloat162_rn(o[nd][2 * i] * mult, o[nd][2 * i + 1] * mult);
+    }
+  }
+}
+
+// Combines the ranges of latent_mma_kernel: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, times the gate.
+// One block per (token, head).
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                    const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out,
+                    int64_t out_stride, int n_tokens, int heads, int rank, int splits) {
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x / heads, head = blockIdx.x - token * heads;
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(((int64_t)s * n_tokens + token) * heads + head) * 2]);
+  float l = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* ml = part_ml + (((int64_t)s * n_tokens + token) * heads + head) * 2;
+    if (ml[0] != -INFINITY) l += fast_exp2(ml[0] - m) * ml[1];
+  }
+  float mult = l > 0.f ? 1.0f / l : 0.f;
+  if (gate) mult *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[token * gate_stride + head])));
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const int64_t base = ((int64_t)s * n_tokens + token) * heads + head;
+      const float ms = part_ml[base * 2];
+      if (ms != -INFINITY) acc += fast_exp2(ms - m) * part_o[base * rank + c];
+    }
+    out[token * out_stride + (int64_t)head * rank + c] = __float2bfloat16_rn(acc * mult);
+  }
+}
+
+template <int RANK, int ROT>
+size_t latent_mma_smem() {
+  return (size_t)LM_BM * (RANK + ROT) * 2 + 2 * (size_t)LM_BN * (RANK + ROT) * 2 + (size_t)LM_BM * (LM_BN + 2) * 4 +
+         (size_t)LM_BM * LM_BN * 2 + 3 * LM_BM * 4;
+}
+
+template <int RANK, int ROT>
+int latent_mma_launch(const __nv_bfloat16* qa, int64_t qa_stride, const __nv_bfloat16* qr, int64_t qr_stride,
+                      int qr_head, const __nv_bfloat16* gate, int64_t gate_stride, __nv_bfloat16* out,
+                      int64_t out_stride, float* part_o, float* part_ml, const __nv_bfloat16* cache,
+                      const int* block_table, int bt_stride, const int* cu_q, const int* ctx_lens, const int* slots,
+                      int num_requests, int max_q_len, int n_tokens, int heads, int block_size, int num_pages,
+                      float scale, int splits, int tiles_per_split, int* status, cudaStream_t stream) {
+  const int gp = heads <= LM_BM ? heads : 1;
+  const int qt = LM_BM / gp;
+  const size_t smem = latent_mma_smem<RANK, ROT>();
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(latent_mma_kernel<RANK, ROT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dim3 grid(((max_q_len + qt - 1) / qt) * splits, heads / gp, num_requests);
+  int code = gllm_launch(latent_mma_kernel<RANK, ROT>, grid, dim3(LM_THREADS), smem, stream, qa, qa_stride, qr,
+                         qr_stride, qr_head, gate, gate_stride, out, out_stride, part_o, part_ml, cache, block_table,
+                         bt_stride, cu_q, ctx_lens, slots, n_tokens, heads, gp, qt, block_size, num_pages,
+                         scale * LOG2E, splits, tiles_per_split, status);
+  if (code != 0 || splits <= 1) return code;
+  return gllm_launch(latent_merge_kernel, dim3((unsigned)(n_tokens * heads)), dim3(128), 0, stream,
+                     (const float*)part_o, (const float*)part_ml, gate, gate_stride, out, out_stride, n_tokens, heads,
+                     RANK, splits);
+}
+}  // namespace
+
+#define GLLM_LATENT_SIZES(X) X(64, 32) X(64, 64) X(96, 32) X(128, 32) X(128, 64) X(256, 32) X(256, 64) X(512, 64)
+
+GLLM_API int gllm_attention_latent_mma_supports(int rank, int rot) {
+#define GLLM_LM_OK(A, B) if (rank == A && rot == B) return 1;
+  GLLM_LATENT_SIZES(GLLM_LM_OK)
+#undef GLLM_LM_OK
+  return 0;
+}
+
+// Query tokens per CTA (the caller sizes its split decision with it).
+GLLM_API int gllm_attention_latent_mma_tokens_per_tile(int heads) { return heads <= LM_BM ? LM_BM / heads : LM_BM; }
+
+GLLM_API int gllm_attention_latent_mma(const __nv_bfloat16* qa, int64_t qa_stride, const __nv_bfloat16* qr,
+                                       int64_t qr_stride, int qr_head, const __nv_bfloat16* gate,
+                                       int64_t gate_stride, __nv_bfloat16* out, int64_t out_stride, float* part_o,
+                                       float* part_ml, const __nv_bfloat16* cache, const int* block_table,
+                                       int bt_stride, const int* cu_q, const int* ctx_lens, const int* slots,
+                                       int num_requests, int max_q_len, int n_tokens, int heads, int rank, int rot,
+                                       int block_size, int num_pages, float scale, int splits, int tiles_per_split,
+                                       int* status, cudaStream_t stream) {
+  if (num_requests <= 0 || max_q_len <= 0) return 0;
+  if (heads <= 0 || num_requests > 65535 || (qa_stride % 8) || (qr_stride % 8) || (qr_head % 8) || (out_stride % 2) ||
+      splits < 1 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || tiles_per_split < 1)))
+    return (int)cudaErrorInvalidValue;
+#define GLLM_LM(A, B)                                                                                              \
+  if (rank == A && rot == B)                                                                                       \
+    return latent_mma_launch<A, B>(qa, qa_stride, qr, qr_stride, qr_head, gate, gate_stride, out, out_stride,      \
+                                   part_o, part_ml, cache, block_table, bt_stride, cu_q, ctx_lens, slots,          \
+                                   num_requests, max_q_len, n_tokens, heads, block_size, num_pages, scale, splits, \
+                                   tiles_per_split, status, stream);
+  GLLM_LATENT_SIZES(GLLM_LM)
+#undef GLLM_LM
+  return (int)cudaErrorInvalidValue;
+}

@@ -53,6 +53,7 @@ MODULES = {
     "attention_sigmoid": "attention_sigmoid.cu",
     "attention_sigmoid_mma": "attention_sigmoid_mma.cu",
     "attention_latent": "attention_latent.cu",
+    "attention_latent_mma": "attention_latent_mma.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

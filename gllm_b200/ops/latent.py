@@ -3,9 +3,76 @@ token.  As everywhere in ``gllm_b200.ops``: CUDA tensors only, no CPU path."""
 
 from __future__ import annotations
 
+import os
+from ctypes import c_float, c_int, c_int64, c_void_p
+
 import torch
 
 from gllm_b200.ops import _check, _cuda, _fn, _ptr, _stream, _suffix, status_word
+from gllm_b200.ops.build import load_module
+
+# GLLM_B200_LATENT_MMA=0: the latent attention of bf16 models stays on the CUDA-core kernel (for measurements)
+USE_TENSOR_CORES = os.environ.get("GLLM_B200_LATENT_MMA", "1") != "0"
+SPLIT_KEYS = 256          # a range of keys is at least this long
+MAX_SPLITS = 32
+KEY_TILE = 32
+_mma = None
+
+
+def _mma_fns():
+    global _mma
+    if _mma is None:
+        lib = load_module("attention_latent_mma")
+        f = lib.gllm_attention_latent_mma
+        P = c_void_p
+        f.argtypes = [P, c_int64, P, c_int64, c_int, P, c_int64, P, c_int64, P, P, P, P, c_int, P, P, P, c_int, c_int,
+                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, P, P]
+        f.restype = c_int
+        lib.gllm_attention_latent_mma_supports.argtypes = [c_int, c_int]
+        lib.gllm_attention_latent_mma_supports.restype = c_int
+        lib.gllm_attention_latent_mma_tokens_per_tile.argtypes = [c_int]
+        lib.gllm_attention_latent_mma_tokens_per_tile.restype = c_int
+        _mma = (f, lib.gllm_attention_latent_mma_supports, lib.gllm_attention_latent_mma_tokens_per_tile)
+    return _mma
+
+
+MMA_SIZES = {(64, 32), (64, 64), (96, 32), (128, 32), (128, 64), (256, 32), (256, 64), (512, 64)}
+
+
+def tensor_core_kernel_takes(dtype: torch.dtype, rank: int, rot: int) -> bool:
+    """True for the (latent, rotated part) widths the tensor-core kernel is built for, in bfloat16."""
+    return dtype == torch.bfloat16 and (rank, rot) in MMA_SIZES and USE_TENSOR_CORES
+
+
+def _attention_latent_mma(qa, rows, q_head, q_plain, gate_col, pages, block_table, heads, rank, rot, block_size, scale,
+                          batch, out):
+    """The tensor-core kernel.  Steps whose tiles do not fill the GPU (single tokens over long contexts) cut every
+    request's keys into ranges of at least ``SPLIT_KEYS`` keys, one CTA each, merged by a second kernel."""
+    f, _, tokens_per_tile = _mma_fns()
+    n = qa.shape[0]
+    qt = tokens_per_tile(heads)
+    tiles = -(-batch.max_q_len // qt) * (1 if heads <= 64 else heads) * batch.num_requests
+    sms = torch.cuda.get_device_properties(qa.device).multi_processor_count
+    splits, tiles_per_split = 1, 0
+    if tiles < sms and batch.max_seq_len > 2 * SPLIT_KEYS:
+        want = min(MAX_SPLITS, -(-2 * sms // tiles))
+        key_tiles = -(-batch.max_seq_len // KEY_TILE)
+        tiles_per_split = max(SPLIT_KEYS // KEY_TILE, -(-key_tiles // want))
+        splits = -(-key_tiles // tiles_per_split)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = batch.workspace.get("latent_attention_partial_out", splits * n * heads * rank, torch.float32)
+        part_ml = batch.workspace.get("latent_attention_partial_max_sum", splits * n * heads * 2, torch.float32)
+    item = qa.element_size()
+    gate_ptr = None if gate_col is None else rows.data_ptr() + gate_col * item
+    code = f(qa.data_ptr(), qa.stride(0), rows.data_ptr() + q_plain * item, rows.stride(0), int(q_head), gate_ptr,
+             rows.stride(0), out.data_ptr(), out.stride(0), _ptr(part_o), _ptr(part_ml), pages.data_ptr(),
+             block_table.data_ptr(), block_table.stride(0), batch.cu_q.data_ptr(), batch.context_lens.data_ptr(),
+             batch.state_slots.data_ptr(), batch.num_requests, batch.max_q_len, n, int(heads), int(rank), int(rot),
+             int(block_size), pages.shape[0], float(scale), splits, tiles_per_split,
+             status_word(qa.device).data_ptr(), _stream())
+    _check(code, "attention_latent_mma")
+    return out
 
 
 def _rows(t: torch.Tensor, name: str, dtype=None) -> None:
@@ -76,6 +143,11 @@ def attention_latent(qa: torch.Tensor, rows: torch.Tensor, q_head: int, q_plain:
     if qa.shape[1] != heads * rank or pages.stride(0) != block_size * (rank + rot):
         raise ValueError("qa or the cache layer does not match heads, rank and rot")
     out = torch.empty((n, heads * rank), dtype=qa.dtype, device=qa.device)
+    if (batch is not None and not window and tensor_core_kernel_takes(qa.dtype, rank, rot) and qa.stride(0) % 8 == 0
+            and rows.stride(0) % 8 == 0 and q_head % 8 == 0 and q_plain % 8 == 0
+            and rows.data_ptr() % 16 == 0 and qa.data_ptr() % 16 == 0):
+        return _attention_latent_mma(qa, rows, q_head, q_plain, gate_col, pages, block_table, heads, rank, rot,
+                                     block_size, scale, batch, out)
     t = _suffix(qa.dtype)
     item = qa.element_size()
     f = _fn("attention_latent", f"gllm_attention_latent_{t}")

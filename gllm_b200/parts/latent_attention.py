@@ -43,7 +43,12 @@ class LatentAttention(Mixer):
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_norm = None
 
     def kernel_needs(self):
-        return {"modules": {"attention_latent"}}
+        from gllm_b200.ops.latent import MMA_SIZES
+
+        modules = {"attention_latent"}
+        if (self.kv_rank, self.rot_dim) in MMA_SIZES:
+            modules.add("attention_latent_mma")          # loaded by bfloat16 runs only
+        return {"modules": modules}
 
     def kv_requirement(self):
         return KVPageRequirement(((1, self.kv_rank + self.rot_dim),), None)

@@ -51,7 +51,7 @@ def steps_of(tokens, cuts, rid="r", first_step=0, end=True):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("mlp", [True, False])
-@pytest.mark.parametrize("kind", ["latent", "window", "causal", "odd"])
+@pytest.mark.parametrize("kind", ["latent", "latent_wide", "latent_many", "window", "causal", "odd"])
 def test_each_mixer_alone(kind, mlp, dtype, tmp_path):
     cfg = single_mixer(kind, mlp)
     weights, _, runner = make(cfg, tmp_path, dtype)
@@ -126,8 +126,8 @@ def test_portions_at_every_edge(name, dtype, tmp_path):
 # mixer maps them to fixed vectors whatever else is in the sequence; head 0's query for token 2 is made to point
 # along head 0's key for token 1 in the part of the head that the rotation leaves alone, and token 1's value is
 # made large.  Every other key scores far lower, so the logits after token 2 say whether token 1's key was seen.
-def decisive_latent_model():
-    cfg = single_mixer("latent", mlp=False)
+def decisive_latent_model(kind="latent"):
+    cfg = single_mixer(kind, mlp=False)
     m = cfg["layers"][0]["mixer"]
     w = draw_weights(cfg, seed=11, sharp=1.0)
     W, d, r, rank, eps = cfg["width"], m["dim"], m["rot_dim"], m["kv_rank"], cfg["norm"]["eps"]
@@ -186,14 +186,18 @@ def check_decisive(cfg, weights, runner, toks, key_at, dtype, seen=True):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_a_far_key_at_page_and_block_edges(dtype, tmp_path):
+@pytest.mark.parametrize("kind", ["latent", "latent_wide"])
+def test_a_far_key_at_page_and_block_edges(kind, dtype, tmp_path):
     from gllm_b200.engine.replay import build_runner
 
-    cfg, weights = decisive_latent_model()
+    cfg, weights = decisive_latent_model(kind)
     folder = write_model(cfg, weights, str(tmp_path / "model"))
     _, runner = build_runner(folder, dtype, 1024, block_size=16)
     g = torch.Generator().manual_seed(5)
     n = 600
+    if dtype == "bfloat16":
+        assert (runner.model.layers[0].mixer.kernel_needs()["modules"] == {"attention_latent", "attention_latent_mma"}) \
+            == (kind == "latent_wide")
     for far in (0, 15, 16, 17, 31, 32, 33, 63, 64, 255, 256, 511):
         toks = torch.randint(3, cfg["vocab"], (n,), generator=g).tolist()
         toks[far], toks[-1] = 1, 2
@@ -390,3 +394,57 @@ def test_one_product_per_head(dtype):
     want = torch.stack([x[:, h * stride:h * stride + i].double() @ w[h].double().T for h in range(heads)], 1)
     tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
     torch.testing.assert_close(got.double(), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("heads,rank,rot", [(5, 64, 32), (16, 128, 64), (70, 96, 32), (3, 512, 64)])
+def test_latent_attention_on_the_tensor_cores_against_the_cuda_cores(heads, rank, rot):
+    """Both kernels over the same pages: prompt portions beside single tokens over long contexts (whose keys are cut
+    into ranges), with a gate; and both against a plain fp64 softmax."""
+    from types import SimpleNamespace
+
+    from gllm_b200.engine.step import Workspace
+    from gllm_b200.ops import latent
+
+    g = torch.Generator().manual_seed(heads)
+    block, dk = 16, rank + rot
+    q_lens, ctx_lens = [37, 1, 1, 5], [70, 900, 0, 333]
+    n, nreq = sum(q_lens), len(q_lens)
+    pages_per = [-(-(c + q) // block) for c, q in zip(ctx_lens, q_lens)]
+    num_pages = sum(pages_per) + 1
+    perm = torch.randperm(num_pages - 1, generator=g).tolist()
+    table = torch.full((nreq + 1, max(pages_per)), -1, dtype=torch.int32)
+    it = iter(perm)
+    for r, k in enumerate(pages_per):
+        table[r, :k] = torch.tensor([next(it) for _ in range(k)], dtype=torch.int32)
+    pool = (torch.randn(num_pages, block * dk, generator=g) * 0.5).to(torch.bfloat16)
+    q_head = 8 + rot
+    width = heads * q_head + heads + 6
+    width += -width % 8
+    rows = torch.randn(n, width, generator=g).to(torch.bfloat16)
+    qa = (torch.randn(n, heads * rank, generator=g) * 0.3).to(torch.bfloat16)
+    gate_col = heads * q_head
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    positions = torch.tensor([c + i for c, q in zip(ctx_lens, q_lens) for i in range(q)], dtype=torch.int32)
+    token_row = torch.tensor([r for r, q in enumerate(q_lens) for _ in range(q)], dtype=torch.int32)
+    batch = SimpleNamespace(max_q_len=max(q_lens), num_requests=nreq, max_seq_len=max(c + q for c, q in zip(ctx_lens, q_lens)),
+                            cu_q=torch.tensor(cu, dtype=torch.int32).cuda(), context_lens=torch.tensor(ctx_lens, dtype=torch.int32).cuda(),
+                            state_slots=torch.arange(nreq, dtype=torch.int32).cuda(), workspace=Workspace("cuda:0"))
+    scale = 0.5 / math.sqrt(dk)
+    args = (qa.cuda(), rows.cuda(), q_head, 8, gate_col, pool.cuda(), table.cuda(), positions.cuda(), token_row.cuda(),
+            heads, rank, rot, block, scale)
+    fast = latent.attention_latent(*args, batch=batch).float().cpu()
+    slow = latent.attention_latent(*args, batch=None).float().cpu()
+    keys = pool.view(num_pages, block, dk).double()
+    want = torch.zeros(n, heads, rank, dtype=torch.float64)
+    for i in range(n):
+        r, p = int(token_row[i]), int(positions[i])
+        k = torch.cat([keys[int(table[r, b])] for b in range(p // block + 1)])[:p + 1]
+        for h in range(heads):
+            q = torch.cat([qa[i, h * rank:(h + 1) * rank], rows[i, h * q_head + 8:(h + 1) * q_head]]).double()
+            w = torch.softmax(k @ q * scale, 0)
+            want[i, h] = (w[:, None] * k[:, :rank]).sum(0) * torch.sigmoid(rows[i, gate_col + h].double())
+    want = want.view(n, heads * rank)
+    torch.testing.assert_close(slow.double(), want, rtol=2e-2, atol=4e-3)
+    torch.testing.assert_close(fast.double(), want, rtol=2e-2, atol=6e-3)

@@ -82,6 +82,8 @@ RULUNEX = {"A": RULUNEX_A, "B": RULUNEX_B, "C": RULUNEX_C, "D": RULUNEX_D}
 def single_mixer(kind: str, mlp: bool = True) -> dict:
     """One layer with the given mixer (and a feed-forward), no repeated stretch."""
     mixer = {"latent": _latent(2, 16, 8, 16, 24, 0.2),
+             "latent_wide": _latent(5, 16, 32, 24, 64, 0.2),        # widths the tensor-core kernel takes
+             "latent_many": _latent(8, 32, 64, 16, 128, 0.12),
              "window": _window(4, 2, 16, 0.25, 8, window=24, scaling=(2.0, 1.0, 4.0, 16)),
              "causal": _window(2, 2, 32, 0.18, 32),
              "odd": _window(3, 1, 20, 0.2, 10, window=9)}[kind]
