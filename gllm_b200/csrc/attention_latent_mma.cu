@@ -132,30 +132,33 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
       __syncthreads();
       const unsigned char* k_sm = k_sm0 + stage * K_BYTES;
       const int kv0 = tile * LM_BN;
-      // ---- S = Q K^T: 16 rows x 16 keys per warp
-      {
-        float s[2][4];
+      // ---- S = Q K^T: 16 rows x 16 keys per warp (a warp whose rows are all unused sits the products out);
+      // even and odd steps along the width add into accumulators of their own: two shorter chains
+      if (rb < rows_used) {
+        float s[2][2][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[c][nt][e] = 0.f;
         const int mat = lane >> 3, rl = lane & 7;
+        const int arow = rb + (mat & 1) * 8 + rl;
+        const int brow = half * 16 + (mat >> 1) * 8 + rl;
 #pragma unroll 4
         for (int ks = 0; ks < DK / 16; ++ks) {
           uint32_t a[4], b[4];
-          const int arow = rb + (mat & 1) * 8 + rl;
           ldmatrix_x4(a, smem_u32(q_sm + (arow * CK + lswz<CK>(arow, 2 * ks + (mat >> 1))) * 16));
-          const int brow = half * 16 + (mat >> 1) * 8 + rl;
           ldmatrix_x4(b, smem_u32(k_sm + (brow * CK + lswz<CK>(brow, 2 * ks + (mat & 1))) * 16));
-          mma_bf16(s[0], a, b[0], b[1]);
-          mma_bf16(s[1], a, b[2], b[3]);
+          mma_bf16(s[ks & 1][0], a, b[0], b[1]);
+          mma_bf16(s[ks & 1][1], a, b[2], b[3]);
         }
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int i = 0; i < 2; ++i)
             *reinterpret_cast<float2*>(s_sm + (rb + g8 + 8 * i) * S_LD + half * 16 + nt * 8 + 2 * t4) =
-                make_float2(s[nt][2 * i], s[nt][2 * i + 1]);
+                make_float2(s[0][nt][2 * i] + s[1][nt][2 * i], s[0][nt][2 * i + 1] + s[1][nt][2 * i + 1]);
       }
       __syncthreads();
       // ---- softmax of the tile: four threads a row
@@ -192,7 +195,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
       }
       __syncthreads();
       // ---- O = O * corr + P V: 16 rows x RANK / 2 columns per warp
-      {
+      if (rb < rows_used) {
         const float c0 = corr_sm[rb + g8], c1 = corr_sm[rb + g8 + 8];
 #pragma unroll
         for (int nd = 0; nd < NV; ++nd) {
@@ -257,30 +260,132 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
 
 // Combines the ranges of latent_mma_kernel: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, times the gate.
 // One block per (token, head).
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out,
                     int64_t out_stride, int n_tokens, int heads, int rank, int splits) {
+  __shared__ float w_s[64];          // weight of every range: 2^(m_s - m) / l, times the gate
   pdl_trigger();
   pdl_wait();
   const int token = blockIdx.x / heads, head = blockIdx.x - token * heads;
-  float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(((int64_t)s * n_tokens + token) * heads + head) * 2]);
-  float l = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* ml = part_ml + (((int64_t)s * n_tokens + token) * heads + head) * 2;
-    if (ml[0] != -INFINITY) l += fast_exp2(ml[0] - m) * ml[1];
+  const int64_t base = (int64_t)token * heads + head, step = (int64_t)n_tokens * heads;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float ms[2], ls[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int s = lane + 32 * k;
+      ms[k] = s < splits ? part_ml[(base + s * step) * 2] : -INFINITY;
+      ls[k] = s < splits ? part_ml[(base + s * step) * 2 + 1] : 0.f;
+    }
+    const float m = warp_max(fmaxf(ms[0], ms[1]));
+    float e[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) e[k] = ms[k] == -INFINITY ? 0.f : fast_exp2(ms[k] - m);
+    const float l = warp_sum(e[0] * ls[0] + e[1] * ls[1]);
+    float mult = l > 0.f ? 1.0f / l : 0.f;
+    if (gate) mult *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[token * gate_stride + head])));
+    w_s[lane] = e[0] * mult;
+    w_s[lane + 32] = e[1] * mult;
   }
-  float mult = l > 0.f ? 1.0f / l : 0.f;
-  if (gate) mult *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[token * gate_stride + head])));
+  __syncthreads();
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const int64_t base = ((int64_t)s * n_tokens + token) * heads + head;
-      const float ms = part_ml[base * 2];
-      if (ms != -INFINITY) acc += fast_exp2(ms - m) * part_o[base * rank + c];
+    for (int s0 = 0; s0 < splits; s0 += 8) {           // eight loads in flight, then eight additions in ascending order
+      float v[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = s0 + k < splits ? __ldcg(part_o + (base + (s0 + k) * step) * rank + c) : 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc = fmaf(w_s[(s0 + k) & 63], v[k], acc);
     }
-    out[token * out_stride + (int64_t)head * rank + c] = __float2bfloat16_rn(acc * mult);
+    out[token * out_stride + (int64_t)head * rank + c] = __float2bfloat16_rn(acc);
+  }
+}
+
+// ------------------------------------------------------------------ one small product per head
+// out[n, h, j] = sum_i x[n, h, i] * w[h, j, i] (the same job as head_linear in attention_latent.cu) on the tensor
+// cores: a CTA of 4 warps owns 64 tokens x 64 outputs of one head, operand tiles of 32 columns come with
+// cp.async in two stages, every warp multiplies its 16 tokens by all 64 outputs.  I a multiple of 8.
+constexpr int HM_BM = 64, HM_BN = 64, HM_BK = 32, HM_THREADS = 128;
+
+__global__ void __launch_bounds__(HM_THREADS)
+head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, int x_head,
+                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, int64_t out_stride,
+                       int out_head, int n_tokens, int I, int J) {
+  constexpr int C = HM_BK / 8;
+  __shared__ __align__(128) unsigned char x_sm[2][HM_BM * HM_BK * 2];
+  __shared__ __align__(128) unsigned char w_sm[2][HM_BN * HM_BK * 2];
+  pdl_trigger();
+  const int m0 = blockIdx.y * HM_BM, n0 = blockIdx.x * HM_BN, h = blockIdx.z;
+  const __nv_bfloat16* xh = x + (int64_t)h * x_head;
+  const __nv_bfloat16* wh = w + (int64_t)h * J * I;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  auto load_w = [&](int k0, int stage) {
+    for (int idx = threadIdx.x; idx < HM_BN * C; idx += HM_THREADS) {
+      const int row = idx / C, piece = idx - row * C;
+      const bool ok = n0 + row < J && k0 + piece * 8 < I;
+      cp_async16(smem_u32(w_sm[stage] + (row * C + lswz<C>(row, piece)) * 16),
+                 ok ? wh + (int64_t)(n0 + row) * I + k0 + piece * 8 : wh, ok);
+    }
+  };
+  auto load_x = [&](int k0, int stage) {
+    for (int idx = threadIdx.x; idx < HM_BM * C; idx += HM_THREADS) {
+      const int row = idx / C, piece = idx - row * C;
+      const bool ok = m0 + row < n_tokens && k0 + piece * 8 < I;
+      cp_async16(smem_u32(x_sm[stage] + (row * C + lswz<C>(row, piece)) * 16),
+                 ok ? xh + (int64_t)(m0 + row) * x_stride + k0 + piece * 8 : xh, ok);
+    }
+  };
+  load_w(0, 0);              // the weight does not depend on the kernel before this one
+  pdl_wait();
+  load_x(0, 0);
+  cp_async_commit();
+  float acc[HM_BN / 8][4];
+#pragma unroll
+  for (int nt = 0; nt < HM_BN / 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+  const int steps = (I + HM_BK - 1) / HM_BK;
+  const int mat = lane >> 3, rl = lane & 7;
+  for (int it = 0; it < steps; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < steps) {
+      load_w((it + 1) * HM_BK, stage ^ 1);
+      load_x((it + 1) * HM_BK, stage ^ 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < HM_BK / 16; ++ks) {
+      uint32_t a[4];
+      const int arow = warp * 16 + (mat & 1) * 8 + rl;
+      ldmatrix_x4(a, smem_u32(x_sm[stage] + (arow * C + lswz<C>(arow, 2 * ks + (mat >> 1))) * 16));
+#pragma unroll
+      for (int np = 0; np < HM_BN / 16; ++np) {
+        uint32_t b[4];
+        const int brow = np * 16 + (mat >> 1) * 8 + rl;
+        ldmatrix_x4(b, smem_u32(w_sm[stage] + (brow * C + lswz<C>(brow, 2 * ks + (mat & 1))) * 16));
+        mma_bf16(acc[2 * np], a, b[0], b[1]);
+        mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + warp * 16 + g8 + 8 * i;
+    if (m >= n_tokens) continue;
+    __nv_bfloat16* dst = out + (int64_t)m * out_stride + (int64_t)h * out_head;
+#pragma unroll
+    for (int nt = 0; nt < HM_BN / 8; ++nt) {
+      const int c = n0 + nt * 8 + 2 * t4;
+      if (c + 1 < J) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(acc[nt][2 * i], acc[nt][2 * i + 1]);
+      else if (c < J) dst[c] = __float2bfloat16_rn(acc[nt][2 * i]);
+    }
   }
 }
 
@@ -311,7 +416,7 @@ int latent_mma_launch(const __nv_bfloat16* qa, int64_t qa_stride, const __nv_bfl
                          bt_stride, cu_q, ctx_lens, slots, n_tokens, heads, gp, qt, block_size, num_pages,
                          scale * LOG2E, splits, tiles_per_split, status);
   if (code != 0 || splits <= 1) return code;
-  return gllm_launch(latent_merge_kernel, dim3((unsigned)(n_tokens * heads)), dim3(128), 0, stream,
+  return gllm_launch(latent_merge_kernel, dim3((unsigned)(n_tokens * heads)), dim3(256), 0, stream,
                      (const float*)part_o, (const float*)part_ml, gate, gate_stride, out, out_stride, n_tokens, heads,
                      RANK, splits);
 }
@@ -339,7 +444,7 @@ GLLM_API int gllm_attention_latent_mma(const __nv_bfloat16* qa, int64_t qa_strid
                                        int* status, cudaStream_t stream) {
   if (num_requests <= 0 || max_q_len <= 0) return 0;
   if (heads <= 0 || num_requests > 65535 || (qa_stride % 8) || (qr_stride % 8) || (qr_head % 8) || (out_stride % 2) ||
-      splits < 1 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || tiles_per_split < 1)))
+      splits < 1 || splits > 64 || (splits > 1 && (part_o == nullptr || part_ml == nullptr || tiles_per_split < 1)))
     return (int)cudaErrorInvalidValue;
 #define GLLM_LM(A, B)                                                                                              \
   if (rank == A && rot == B)                                                                                       \
@@ -350,4 +455,17 @@ GLLM_API int gllm_attention_latent_mma(const __nv_bfloat16* qa, int64_t qa_strid
   GLLM_LATENT_SIZES(GLLM_LM)
 #undef GLLM_LM
   return (int)cudaErrorInvalidValue;
+}
+
+GLLM_API int gllm_head_linear_mma(const __nv_bfloat16* x, int64_t x_stride, int x_head, const __nv_bfloat16* w,
+                                  __nv_bfloat16* out, int64_t out_stride, int out_head, int n_tokens, int heads, int I,
+                                  int J, cudaStream_t stream) {
+  if (n_tokens <= 0 || heads <= 0) return 0;
+  if (I <= 0 || J <= 0 || heads > 65535 || (I % 8) || (x_stride % 8) || (x_head % 8) || (out_stride % 2) ||
+      (out_head % 2))
+    return (int)cudaErrorInvalidValue;
+  const dim3 grid((J + HM_BN - 1) / HM_BN, (n_tokens + HM_BM - 1) / HM_BM, heads);
+  if (grid.y > 65535) return (int)cudaErrorInvalidValue;
+  return gllm_launch(head_linear_mma_kernel, grid, dim3(HM_THREADS), 0, stream, x, x_stride, x_head, w, out,
+                     out_stride, out_head, n_tokens, I, J);
 }

@@ -28,6 +28,19 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(f
   return __float2bfloat16_rn(v);
 }
 
+// The gate of a gated feed-forward: a(g) * (u + offset) with a(g) = g * sigmoid(slope * g), after
+// g = min(g, limit) and u = clamp(u, -limit, limit) when limit > 0.  {1, 0, 0} is silu(g) * u.
+struct GateAct {
+  float slope, limit, offset;
+};
+__device__ __forceinline__ float gate_act(float g, float u, const GateAct& a) {
+  if (a.limit > 0.f) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+  }
+  return g / (1.0f + __expf(-a.slope * g)) * (u + a.offset);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -1003,11 +1003,27 @@ residual_add_kernel(const T* __restrict__ branch, const float* __restrict__ part
     resid[i] = x;
   }
 }
+// The plain add, four columns a thread (a branch tensor, 16-byte aligned operands, a multiple of 4 elements).
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_add4_kernel(const T* __restrict__ branch, float* __restrict__ resid, int64_t total4) {
+  pdl_trigger();
+  pdl_wait();
+  const int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (i >= total4) return;
+  float4 x = reinterpret_cast<float4*>(resid)[i];
+  const T* b = branch + 4 * i;
+  x.x += to_float(b[0]); x.y += to_float(b[1]); x.z += to_float(b[2]); x.w += to_float(b[3]);
+  reinterpret_cast<float4*>(resid)[i] = x;
+}
 #define GLLM_RESIDUAL_EXPORTS(T, S)                                                                              \
   GLLM_API int gllm_residual_add_##S(const T* branch, const float* parts, int n_parts, int64_t part_stride,     \
                                      float* resid, int64_t total, cudaStream_t stream) {                        \
     if (total <= 0) return 0;                                                                                    \
     if (n_parts > 16) return (int)cudaErrorInvalidValue;                                                         \
+    if (branch && !parts && total % 4 == 0 && aligned16(resid) && (reinterpret_cast<uintptr_t>(branch) & 7) == 0) \
+      return gllm_launch(residual_add4_kernel<T>, dim3((unsigned)((total / 4 + 255) / 256)), dim3(256), 0, stream, \
+                         branch, resid, total / 4);                                                              \
     return gllm_launch(residual_add_kernel<T, false>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,       \
                        stream, branch, parts, n_parts, part_stride, resid, (const float*)nullptr, (T*)nullptr,   \
                        total, 1);                                                                                \
@@ -1032,7 +1048,7 @@ GLLM_RESIDUAL_EXPORTS(__nv_bfloat16, bf16)
 //   v  = k as projected (with `values_from_keys`; otherwise src has a v projection after k, which is copied)
 // wq / wk null: that projection is copied un-normed.  Statistics in fp32.  One block per token.
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 qk_rownorm_kernel(const T* __restrict__ src, int64_t src_stride, const float* __restrict__ parts, int n_parts,
                   int64_t part_stride, const float* __restrict__ wq, const float* __restrict__ wk,
                   T* __restrict__ dst, int n_tokens, int q_cols, int k_cols, int values_from_keys, float eps) {
@@ -1081,7 +1097,8 @@ qk_rownorm_kernel(const T* __restrict__ src, int64_t src_stride, const float* __
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;                                                    \
     if (smem > 48 * 1024)                                                                                        \
       cudaFuncSetAttribute(qk_rownorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-    return gllm_launch(qk_rownorm_kernel<T>, dim3((unsigned)n_tokens), dim3(256), smem, stream, src, src_stride, \
+    const int threads = (q_cols + k_cols >= 2048 && n_tokens <= 64) ? 1024 : 256;                                \
+    return gllm_launch(qk_rownorm_kernel<T>, dim3((unsigned)n_tokens), dim3(threads), smem, stream, src, src_stride, \
                        parts, n_parts, part_stride, wq, wk, dst, n_tokens, q_cols, k_cols, values_from_keys, eps); \
   }
 GLLM_QK_ROWNORM_EXPORTS(float, f32)

@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
                  int tiles_a, int num_items, float* __restrict__ partial, int* __restrict__ tickets,
-                 int reduce_in_kernel, int* __restrict__ status, int accumulate) {
+                 int reduce_in_kernel, int* __restrict__ status, int accumulate, GateAct act) {
   using S = Shape<BN>;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
@@ -262,7 +262,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (m < M && f0 < n_out) {
               float y[16];
 #pragma unroll
-              for (int i = 0; i < 16; ++i) y[i] = g[i] / (1.0f + __expf(-g[i])) * u[i];
+              for (int i = 0; i < 16; ++i) y[i] = gate_act(g[i], u[i], act);
               OutT* dst = out + (int64_t)m * ldo + f0;
               if (f0 + 16 <= n_out && sizeof(OutT) == 2 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
                 uint4 p0, p1;
@@ -308,7 +308,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (m < M) {
                   const float mine_v = row < 64 ? v[i] : v[CH - 16 + i], other = exch[row & 63][c + off + i];
                   const float g = row < 64 ? mine_v : other, u = row < 64 ? other : mine_v;
-                  out[(int64_t)m * ldo + f] = cast_out<OutT>(g / (1.0f + __expf(-g)) * u);
+                  out[(int64_t)m * ldo + f] = cast_out<OutT>(gate_act(g, u, act));
                 }
               }
             }
@@ -464,7 +464,7 @@ int sm_count() { return gllm_sm_count(); }
 template <int BN, bool SWAPPED, typename OutT, bool GATED>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                 int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
-                cudaStream_t stream, int accumulate = 0) {
+                cudaStream_t stream, int accumulate = 0, GateAct act = GateAct{1.f, 0.f, 0.f}) {
   using S = Shape<BN>;
   CUtensorMap map_a, map_b;
   const bool ok = SWAPPED ? (make_map(&map_a, W, N, K, ldw, BM) && make_map(&map_b, X, M, K, ldx, BN))
@@ -485,7 +485,7 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int grid = num_items < sm_count() ? num_items : sm_count();
   return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT, GATED>, dim3(grid), dim3(THREADS), (size_t)S::SMEM, stream, map_a,
                      map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets,
-                     reduce_in_kernel, status, accumulate);
+                     reduce_in_kernel, status, accumulate, act);
 }
 
 // Width of the weight tile for more than 64 tokens: 256 rows; 64 for a single tile of tokens (65 .. 128) times a
@@ -503,10 +503,10 @@ static int normal_tile_rows(int M, int N, bool gated) {
 template <typename OutT, bool GATED>
 int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                   int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, GateAct act = GateAct{1.f, 0.f, 0.f}) {
 #define GLLM_UMMA(BN, SW) \
   return umma_launch<BN, SW, OutT, GATED>(X, W, out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel, \
-                                   status, stream)
+                                   status, stream, 0, act)
   if (M <= 16) GLLM_UMMA(16, true);
   if (M <= 32) GLLM_UMMA(32, true);
   if (M <= 64) GLLM_UMMA(64, true);
@@ -573,15 +573,17 @@ GLLM_API int gllm_gemm_bf16(const __nv_bfloat16* X, const __nv_bfloat16* W, void
 // The gated feed-forward's first product with SiLU(gate) * up in the epilogue: W is [2*I, K] with
 // rows in blocks of 64 gate rows followed by the 64 up rows of the same features (I % 64 == 0);
 // out is [M, I] bf16.  Never cut along K.
+// slope, limit, offset: the activation a(g) * (u + offset), a(g) = g * sigmoid(slope * g), with the gate capped
+// at limit and the up product clamped to [-limit, limit] when limit > 0 (1, 0, 0: SiLU(gate) * up).
 GLLM_API int gllm_gemm_bf16_gated(const __nv_bfloat16* X, const __nv_bfloat16* W, __nv_bfloat16* out, int M,
-                                  int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int* status,
-                                  cudaStream_t stream) {
+                                  int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, float slope, float limit,
+                                  float offset, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || N % 128 || (reinterpret_cast<uintptr_t>(X) & 15) ||
       (reinterpret_cast<uintptr_t>(W) & 15))
     return (int)cudaErrorInvalidValue;
   return umma_dispatch<__nv_bfloat16, true>(X, W, out, M, N, K, ldx, ldw, ldo, 1, nullptr, nullptr, 0, status,
-                                            stream);
+                                            stream, GateAct{slope, limit, offset});
 }
 
 // The product of few tokens (M <= 64) added into an fp32 matrix: acc[M, N] += X[M, K] * W[N, K]^T, each

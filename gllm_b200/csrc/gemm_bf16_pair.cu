@@ -83,7 +83,7 @@ template <typename OutT, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                       OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int tiles_m, int num_items,
-                      int* __restrict__ status) {
+                      int* __restrict__ status, GateAct act) {
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
@@ -236,7 +236,7 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
           if (m < M && f0 < n_out) {
             float y[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) y[i] = g[i] / (1.0f + __expf(-g[i])) * u[i];
+            for (int i = 0; i < 16; ++i) y[i] = gate_act(g[i], u[i], act);
             OutT* dst = out + (int64_t)m * ldo + f0;
             if (f0 + 16 <= n_out && sizeof(OutT) == 2 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
               uint4 p0, p1;
@@ -331,7 +331,7 @@ int sm_count() { return gllm_sm_count(); }
 
 template <typename OutT, bool GATED>
 int pair_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
-                int64_t ldw, int64_t ldo, int* status, cudaStream_t stream) {
+                int64_t ldw, int64_t ldo, int* status, cudaStream_t stream, GateAct act = GateAct{1.f, 0.f, 0.f}) {
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, X, M, K, ldx, BM) || !make_map(&map_w, W, N, K, ldw, BNH)) return (int)cudaErrorInvalidValue;
   static bool attr_set = false;
@@ -345,22 +345,24 @@ int pair_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int num_items = tiles_m * tiles_n;
   const int pairs = num_items < sm_count() / 2 ? num_items : sm_count() / 2;
   return gllm_launch_cluster(umma_gemm_pair_kernel<OutT, GATED>, dim3(2 * pairs), dim3(THREADS), (size_t)SMEM, stream,
-                             2u, map_x, map_w, out, M, N, K, ldo, tiles_m, num_items, status);
+                             2u, map_x, map_w, out, M, N, K, ldo, tiles_m, num_items, status, act);
 }
 }  // namespace
 
 // out_is_f32: 0 = bf16 output, 1 = fp32 output; gated != 0: W is [2*I, K] in blocks of 64 gate rows and
 // the 64 up rows of the same features (N = 2*I, I % 64 == 0), out is [M, I] bf16.  Needs K % 8 == 0
-// and 16-byte aligned rows of X and W.
+// and 16-byte aligned rows of X and W.  slope, limit, offset: the gated form's activation (1, 0, 0: SiLU(gate) * up;
+// see GateAct).
 GLLM_API int gllm_gemm_bf16_pair(const __nv_bfloat16* X, const __nv_bfloat16* W, void* out, int out_is_f32, int gated,
-                                 int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int* status,
-                                 cudaStream_t stream) {
+                                 int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, float slope, float limit,
+                                 float offset, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || (reinterpret_cast<uintptr_t>(X) & 15) ||
       (reinterpret_cast<uintptr_t>(W) & 15) || (gated && (out_is_f32 || N % 128)))
     return (int)cudaErrorInvalidValue;
   if (gated)
-    return pair_launch<__nv_bfloat16, true>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, status, stream);
+    return pair_launch<__nv_bfloat16, true>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, status, stream,
+                                            GateAct{slope, limit, offset});
   if (out_is_f32) return pair_launch<float, false>(X, W, (float*)out, M, N, K, ldx, ldw, ldo, status, stream);
   return pair_launch<__nv_bfloat16, false>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, status, stream);
 }

@@ -12,7 +12,7 @@ which is what the reference uses for every projection
 from __future__ import annotations
 
 import os
-from ctypes import c_int, c_int64, c_void_p
+from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
 
@@ -37,7 +37,7 @@ def _umma_fns():
         lib.gllm_gemm_bf16_tiles.argtypes = [c_int, c_int]
         lib.gllm_gemm_bf16_tiles.restype = c_int
         g = lib.gllm_gemm_bf16_gated
-        g.argtypes = [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, P, P]
+        g.argtypes = [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_float, c_float, c_float, P, P]
         g.restype = c_int
         _umma = (f, lib.gllm_gemm_bf16_splits, lib.gllm_gemm_bf16_tiles, g)
     return _umma
@@ -125,20 +125,22 @@ def _pair_fn():
     if _pair is None:
         lib = load_module("gemm_bf16_pair")
         f = lib.gllm_gemm_bf16_pair
-        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, P, P]
+        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_float, c_float, c_float,
+                      P, P]
         f.restype = c_int
         _pair = f
     return _pair
 
 
-def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> torch.Tensor:
+def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+                act: tuple = (1.0, 0.0, 0.0)) -> torch.Tensor:
     """``out = x @ weight.T`` (or its gated form, see ``linear_gated``) by the kernel in which two CTAs
     of a cluster share every 256x256 tile.  Any number of tokens is right; few are slow."""
     from gllm_b200 import ops
 
     m, k = x.shape
     code = _pair_fn()(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), int(gated), m,
-                      weight.shape[0], k, x.stride(0), weight.stride(0), out.stride(0),
+                      weight.shape[0], k, x.stride(0), weight.stride(0), out.stride(0), *act,
                       ops.status_word(x.device).data_ptr(), ops._stream())
     ops._check(code, "gemm_bf16_pair")
     return out
@@ -209,13 +211,13 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> tor
 
 def linear_gated(x: torch.Tensor, weight: torch.Tensor, slope: float = 1.0, limit: float | None = None,
                  up_offset: float = 0.0):
-    """``silu(gate) * up`` of a weight stacked in blocks of 64 gate / 64 up rows, fused into the
-    product's epilogue; None when the kernel does not take these operands (or another activation
-    than the plain one is asked for)."""
+    """``a(gate) * (up + up_offset)`` of a weight stacked in blocks of 64 gate / 64 up rows, fused into the
+    product's epilogue (``a(g) = g * sigmoid(slope * g)``, gate capped at ``limit`` and up clamped to
+    ``[-limit, limit]`` with ``limit``; the defaults are ``silu(gate) * up``); None when the kernel does not take
+    these operands."""
     from gllm_b200 import ops
 
-    if slope != 1.0 or limit is not None or up_offset != 0.0:
-        return None
+    act = (float(slope), float(limit or 0.0), float(up_offset))
 
     n, k = weight.shape
     if not tensor_core_kernel_takes(x, weight) or n % 128:
@@ -223,10 +225,10 @@ def linear_gated(x: torch.Tensor, weight: torch.Tensor, slope: float = 1.0, limi
     m = x.shape[0]
     out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
     if pair_kernel_pays(x, n):
-        return linear_pair(x, weight, out, gated=True)
+        return linear_pair(x, weight, out, gated=True, act=act)
     g = _umma_fns()[3]
     code = g(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), weight.stride(0), out.stride(0),
-             ops.status_word(x.device).data_ptr(), ops._stream())
+             *act, ops.status_word(x.device).data_ptr(), ops._stream())
     ops._check(code, "gemm_bf16_gated")
     return out
 

@@ -13,8 +13,8 @@ from gllm_b200.ops.build import load_module
 
 # GLLM_B200_LATENT_MMA=0: the latent attention of bf16 models stays on the CUDA-core kernel (for measurements)
 USE_TENSOR_CORES = os.environ.get("GLLM_B200_LATENT_MMA", "1") != "0"
-SPLIT_KEYS = 256          # a range of keys is at least this long
-MAX_SPLITS = 32
+SPLIT_KEYS = 64           # a range of keys is at least this long
+MAX_SPLITS = 64
 KEY_TILE = 32
 _mma = None
 
@@ -32,7 +32,10 @@ def _mma_fns():
         lib.gllm_attention_latent_mma_supports.restype = c_int
         lib.gllm_attention_latent_mma_tokens_per_tile.argtypes = [c_int]
         lib.gllm_attention_latent_mma_tokens_per_tile.restype = c_int
-        _mma = (f, lib.gllm_attention_latent_mma_supports, lib.gllm_attention_latent_mma_tokens_per_tile)
+        hl = lib.gllm_head_linear_mma
+        hl.argtypes = [P, c_int64, c_int, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, P]
+        hl.restype = c_int
+        _mma = (f, lib.gllm_attention_latent_mma_supports, lib.gllm_attention_latent_mma_tokens_per_tile, hl)
     return _mma
 
 
@@ -48,7 +51,7 @@ def _attention_latent_mma(qa, rows, q_head, q_plain, gate_col, pages, block_tabl
                           batch, out):
     """The tensor-core kernel.  Steps whose tiles do not fill the GPU (single tokens over long contexts) cut every
     request's keys into ranges of at least ``SPLIT_KEYS`` keys, one CTA each, merged by a second kernel."""
-    f, _, tokens_per_tile = _mma_fns()
+    f, _, tokens_per_tile = _mma_fns()[:3]
     n = qa.shape[0]
     qt = tokens_per_tile(heads)
     tiles = -(-batch.max_q_len // qt) * (1 if heads <= 64 else heads) * batch.num_requests
@@ -119,6 +122,12 @@ def head_linear(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.T
     n = x.shape[0]
     if out is None:
         out = torch.empty((n, heads * j), dtype=x.dtype, device=x.device)
+    if (x.dtype == torch.bfloat16 and USE_TENSOR_CORES and i % 8 == 0 and x.stride(0) % 8 == 0 and x_head % 8 == 0
+            and j % 2 == 0 and out.stride(0) % 2 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0
+            and out.data_ptr() % 4 == 0):
+        _check(_mma_fns()[3](x.data_ptr(), x.stride(0), int(x_head), weight.data_ptr(), out.data_ptr(), out.stride(0), j,
+                             n, heads, i, j, _stream()), "head_linear_mma")
+        return out
     f = _fn("attention_latent", f"gllm_head_linear_{_suffix(x.dtype)}")
     _check(f(x.data_ptr(), x.stride(0), int(x_head), weight.data_ptr(), out.data_ptr(), out.stride(0), j, n, heads, i,
              j, _stream()), "head_linear")

@@ -43,12 +43,8 @@ class LatentAttention(Mixer):
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.c_norm = None
 
     def kernel_needs(self):
-        from gllm_b200.ops.latent import MMA_SIZES
-
-        modules = {"attention_latent"}
-        if (self.kv_rank, self.rot_dim) in MMA_SIZES:
-            modules.add("attention_latent_mma")          # loaded by bfloat16 runs only
-        return {"modules": modules}
+        # the second module holds the tensor-core kernels of bfloat16 runs
+        return {"modules": {"attention_latent", "attention_latent_mma"}}
 
     def kv_requirement(self):
         return KVPageRequirement(((1, self.kv_rank + self.rot_dim),), None)

@@ -196,8 +196,10 @@ def test_a_far_key_at_page_and_block_edges(kind, dtype, tmp_path):
     g = torch.Generator().manual_seed(5)
     n = 600
     if dtype == "bfloat16":
-        assert (runner.model.layers[0].mixer.kernel_needs()["modules"] == {"attention_latent", "attention_latent_mma"}) \
-            == (kind == "latent_wide")
+        from gllm_b200.ops import latent
+
+        m = cfg["layers"][0]["mixer"]
+        assert latent.tensor_core_kernel_takes(torch.bfloat16, m["kv_rank"], m["rot_dim"]) == (kind == "latent_wide")
     for far in (0, 15, 16, 17, 31, 32, 33, 63, 64, 255, 256, 511):
         toks = torch.randint(3, cfg["vocab"], (n,), generator=g).tolist()
         toks[far], toks[-1] = 1, 2
@@ -383,12 +385,12 @@ def test_residual_add_and_join(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_one_product_per_head(dtype):
+@pytest.mark.parametrize("n,heads,i,j,stride", [(70, 3, 20, 37, 29), (1, 4, 64, 24, 96), (150, 3, 136, 70, 144)])
+def test_one_product_per_head(dtype, n, heads, i, j, stride):
     from gllm_b200.ops import latent
 
     g = torch.Generator().manual_seed(4)
-    n, heads, i, j, stride = 70, 3, 20, 37, 29
-    x = torch.randn(n, heads * stride + 5, generator=g).to(dtype)
+    x = torch.randn(n, heads * stride + 8, generator=g).to(dtype)
     w = torch.randn(heads, j, i, generator=g).to(dtype)
     got = latent.head_linear(x.cuda(), stride, w.cuda()).float().cpu().view(n, heads, j)
     want = torch.stack([x[:, h * stride:h * stride + i].double() @ w[h].double().T for h in range(heads)], 1)
