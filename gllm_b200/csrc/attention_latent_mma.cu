@@ -25,22 +25,35 @@ __device__ __forceinline__ int lswz(int row, int piece) {
   return piece ^ ((row >> 1) & 3);
 }
 
-template <int RANK, int ROT>
-__global__ void __launch_bounds__(LM_THREADS)
+__device__ __forceinline__ void ldmatrix_x2(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+// FEW: no CTA of the launch has more than 16 rows (single tokens of up to 16 heads).  The eight warps then share
+// the one block of 16 rows: in S = Q K^T a warp takes 8 of the tile's keys and one half of the width (the halves
+// are added by the softmax threads), in P V it takes every eighth block of 16 value columns.  The accumulators are
+// a quarter of the general form's, so that two CTAs fit an SM.
+template <int RANK, int ROT, bool FEW>
+__global__ void __launch_bounds__(LM_THREADS, FEW ? 2 : 1)
 latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const __nv_bfloat16* __restrict__ qr,
                   int64_t qr_stride, int qr_head, const __nv_bfloat16* __restrict__ gate, int64_t gate_stride,
                   __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ part_o,
                   float* __restrict__ part_ml, const __nv_bfloat16* __restrict__ cache,
                   const int* __restrict__ block_table, int bt_stride, const int* __restrict__ cu_q,
                   const int* __restrict__ ctx_lens, const int* __restrict__ slots, int n_tokens, int heads, int gp,
-                  int qt, int block_size, int num_pages, float scale_log2, int splits, int tiles_per_split,
-                  int* __restrict__ status) {
+                  int qt, int q_rows, int block_size, int num_pages, float scale_log2, int splits,
+                  int tiles_per_split, int* __restrict__ status) {
   constexpr int DK = RANK + ROT, CK = DK / 8, CR = RANK / 8, CP = LM_BN / 8;
-  constexpr int Q_BYTES = LM_BM * DK * 2, K_BYTES = LM_BN * DK * 2;
+  constexpr int K_BYTES = LM_BN * DK * 2;
+  // q_rows: a multiple of 16 that no CTA of the launch uses more rows than (16 for single tokens of 16 heads: the
+  // queries then take a quarter of the room and two CTAs fit an SM)
+  const int Q_BYTES = q_rows * DK * 2;
   constexpr int S_LD = LM_BN + 2;
-  constexpr int NV = RANK / 16;            // n8 tiles of a warp's half of the value columns
+  constexpr int NV = FEW ? 2 : RANK / 16;  // n8 tiles of a warp's half of the value columns
+  constexpr int PAIRS = RANK / 16;         // FEW: blocks of 16 value columns, dealt out to the warps in turn
+  constexpr int MAXP = FEW ? (PAIRS + 7) / 8 : 1;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  unsigned char* q_sm = smem_raw;                                   // [64][DK] bf16
+  unsigned char* q_sm = smem_raw;                                   // [q_rows][DK] bf16
   unsigned char* k_sm0 = q_sm + Q_BYTES;                            // 2 x [32][DK] bf16
   float* s_sm = reinterpret_cast<float*>(k_sm0 + 2 * K_BYTES);      // [64][S_LD]
   unsigned char* p_sm = reinterpret_cast<unsigned char*>(s_sm + LM_BM * S_LD);   // [64][32] bf16
@@ -86,36 +99,45 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
   for (int nd = 0; nd < NV; ++nd)
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[nd][e] = 0.f;
+  float of[MAXP][2][4];
+#pragma unroll
+  for (int j = 0; j < MAXP; ++j)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) of[j][nt][e] = 0.f;
 
   if (tile_first <= tile_last) {
-    for (int idx = threadIdx.x; idx < LM_BM * CK; idx += LM_THREADS) {
-      const int rr = idx / CK, piece = idx - rr * CK;
-      const int tl = rr / gp, g = rr - tl * gp;
-      const bool ok = rr < rows_used;
-      const int64_t token = tok_begin + t0 + (ok ? tl : 0);
-      const __nv_bfloat16* src = piece < CR
-          ? qa + token * qa_stride + (int64_t)(h0 + (ok ? g : 0)) * RANK + piece * 8
-          : qr + token * qr_stride + (int64_t)(h0 + (ok ? g : 0)) * qr_head + (piece - CR) * 8;
-      cp_async16(smem_u32(q_sm + (rr * CK + lswz<CK>(rr, piece)) * 16), src, ok);
-    }
-    auto load_k = [&](int tile, int stage) {
-      unsigned char* dst = k_sm0 + stage * K_BYTES;
-      for (int idx = threadIdx.x; idx < LM_BN * CK; idx += LM_THREADS) {
-        const int row = idx / CK, piece = idx - row * CK;
-        const int key = tile * LM_BN + row;
-        bool ok = key <= pos_last;
-        int page = 0;
-        if (ok) {
-          page = bt[key / block_size];
-          if (page < 0 || page >= num_pages) {
-            atomicOr(status, GLLM_STATUS_PAGE_RANGE);
-            ok = false;
-            page = 0;
-          }
-        }
-        const __nv_bfloat16* src = cache + ((int64_t)page * block_size + key % block_size) * DK + piece * 8;
-        cp_async16(smem_u32(dst + (row * CK + lswz<CK>(row, piece)) * 16), ok ? src : cache, ok);
+    {   // four threads a row: one division per thread
+      const int rr = threadIdx.x >> 2;
+      if (rr < q_rows) {
+        const int tl = rr / gp, g = rr - tl * gp;
+        const bool ok = rr < rows_used;
+        const int64_t token = tok_begin + t0 + (ok ? tl : 0);
+        const __nv_bfloat16* a_src = qa + token * qa_stride + (int64_t)(h0 + (ok ? g : 0)) * RANK;
+        const __nv_bfloat16* r_src = qr + token * qr_stride + (int64_t)(h0 + (ok ? g : 0)) * qr_head;
+        for (int piece = threadIdx.x & 3; piece < CK; piece += 4)
+          cp_async16(smem_u32(q_sm + (rr * CK + lswz<CK>(rr, piece)) * 16),
+                     piece < CR ? a_src + piece * 8 : r_src + (piece - CR) * 8, ok);
       }
+    }
+    auto load_k = [&](int tile, int stage) {     // eight threads a key: one look-up of its page per thread
+      unsigned char* dst = k_sm0 + stage * K_BYTES;
+      const int row = threadIdx.x >> 3;
+      const int key = tile * LM_BN + row;
+      bool ok = key <= pos_last;
+      int page = 0;
+      if (ok) {
+        page = bt[key / block_size];
+        if (page < 0 || page >= num_pages) {
+          atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+          ok = false;
+          page = 0;
+        }
+      }
+      const __nv_bfloat16* src = ok ? cache + ((int64_t)page * block_size + key % block_size) * DK : cache;
+      for (int piece = threadIdx.x & 7; piece < CK; piece += 8)
+        cp_async16(smem_u32(dst + (row * CK + lswz<CK>(row, piece)) * 16), ok ? src + piece * 8 : cache, ok);
     };
     load_k(tile_first, 0);
     cp_async_commit();
@@ -134,7 +156,35 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
       const int kv0 = tile * LM_BN;
       // ---- S = Q K^T: 16 rows x 16 keys per warp (a warp whose rows are all unused sits the products out);
       // even and odd steps along the width add into accumulators of their own: two shorter chains
-      if (rb < rows_used) {
+      if constexpr (FEW) {
+        float s2[2][4];
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s2[c][e] = 0.f;
+        constexpr int KS_HALF = DK / 32;
+        const int mat = lane >> 3, rl = lane & 7;
+        const int arow = (mat & 1) * 8 + rl;
+        const int key8 = (warp & 3) * 8, kh = warp >> 2;
+        const int brow = key8 + rl;
+        auto step = [&](int k, float (&acc)[4]) {
+          const int ks = kh * KS_HALF + k;
+          uint32_t a[4], b0, b1;
+          ldmatrix_x4(a, smem_u32(q_sm + (arow * CK + lswz<CK>(arow, 2 * ks + (mat >> 1))) * 16));
+          ldmatrix_x2(b0, b1, smem_u32(k_sm + (brow * CK + lswz<CK>(brow, 2 * ks + (mat & 1))) * 16));
+          mma_bf16(acc, a, b0, b1);
+        };
+#pragma unroll 2
+        for (int k = 0; k + 1 < KS_HALF; k += 2) {       // two chains of additions
+          step(k, s2[0]);
+          step(k + 1, s2[1]);
+        }
+        if (KS_HALF & 1) step(KS_HALF - 1, s2[0]);
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          *reinterpret_cast<float2*>(s_sm + (kh * 16 + g8 + 8 * i) * S_LD + key8 + 2 * t4) =
+              make_float2(s2[0][2 * i] + s2[1][2 * i], s2[0][2 * i + 1] + s2[1][2 * i + 1]);
+      } else if (rb < rows_used) {
         float s[2][2][4];
 #pragma unroll
         for (int c = 0; c < 2; ++c)
@@ -162,13 +212,15 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
       }
       __syncthreads();
       // ---- softmax of the tile: four threads a row
-      {
+      if (!FEW || warp < 2) {
         float v[8];
         float mx = -INFINITY;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int key = kv0 + squart * 8 + e;
-          const float x = s_sm[srow * S_LD + squart * 8 + e] * scale_log2;
+          float x = s_sm[srow * S_LD + squart * 8 + e];
+          if (FEW) x += s_sm[(16 + srow) * S_LD + squart * 8 + e];      // the other half of the width
+          x *= scale_log2;
           v[e] = (s_ok && key <= s_qpos) ? x : -INFINITY;
           mx = fmaxf(mx, v[e]);
         }
@@ -195,7 +247,33 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
       }
       __syncthreads();
       // ---- O = O * corr + P V: 16 rows x RANK / 2 columns per warp
-      if (rb < rows_used) {
+      if constexpr (FEW) {
+        const float c0 = corr_sm[g8], c1 = corr_sm[g8 + 8];
+#pragma unroll
+        for (int j = 0; j < MAXP; ++j)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            of[j][nt][0] *= c0; of[j][nt][1] *= c0; of[j][nt][2] *= c1; of[j][nt][3] *= c1;
+          }
+        const int mat = lane >> 3, rl = lane & 7;
+#pragma unroll
+        for (int kk = 0; kk < LM_BN / 16; ++kk) {
+          uint32_t a[4];
+          const int arow = (mat & 1) * 8 + rl;
+          ldmatrix_x4(a, smem_u32(p_sm + (arow * CP + lswz<CP>(arow, 2 * kk + (mat >> 1))) * 16));
+#pragma unroll
+          for (int j = 0; j < MAXP; ++j) {
+            const int pair = warp + 8 * j;
+            if (pair < PAIRS) {
+              const int row = kk * 16 + (mat & 1) * 8 + rl;
+              uint32_t b[4];
+              ldmatrix_x4_trans(b, smem_u32(k_sm + (row * CK + lswz<CK>(row, 2 * pair + (mat >> 1))) * 16));
+              mma_bf16(of[j][0], a, b[0], b[1]);
+              mma_bf16(of[j][1], a, b[2], b[3]);
+            }
+          }
+        }
+      } else if (rb < rows_used) {
         const float c0 = corr_sm[rb + g8], c1 = corr_sm[rb + g8 + 8];
 #pragma unroll
         for (int nd = 0; nd < NV; ++nd) {
@@ -227,6 +305,41 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
   }
   __syncthreads();
   // ---- store
+  if constexpr (FEW) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int rr = g8 + 8 * i;
+      if (rr >= rows_used) continue;
+      const int tl = rr / gp, g = rr - tl * gp;
+      const int64_t token = tok_begin + t0 + tl;
+      const int head = h0 + g;
+      float mult = 1.f;
+      if (splits == 1) {
+        const float l = l_sm[rr];
+        mult = l > 0.f ? 1.0f / l : 0.f;
+        if (gate) mult *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[token * gate_stride + head])));
+      } else if (warp == 0 && t4 == 0) {
+        float* ml = part_ml + (((int64_t)split * n_tokens + token) * heads + head) * 2;
+        ml[0] = m_sm[rr];
+        ml[1] = l_sm[rr];
+      }
+#pragma unroll
+      for (int j = 0; j < MAXP; ++j) {
+        const int pair = warp + 8 * j;
+        if (pair >= PAIRS) continue;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const int col = pair * 16 + nt * 8 + 2 * t4;
+          if (splits > 1)
+            *reinterpret_cast<float2*>(part_o + (((int64_t)split * n_tokens + token) * heads + head) * RANK + col) =
+                make_float2(of[j][nt][2 * i], of[j][nt][2 * i + 1]);
+          else
+            *reinterpret_cast<__nv_bfloat162*>(out + token * out_stride + (int64_t)head * RANK + col) =
+                __floats2bfloat162_rn(of[j][nt][2 * i] * mult, of[j][nt][2 * i + 1] * mult);
+        }
+      }
+    }
+  } else {
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int rr = rb + g8 + 8 * i;
@@ -255,6 +368,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
         *reinterpret_cast<__nv_bfloat162*>(dst + nd * 8 + 2 * t4) =
             __floats2bfloat162_rn(o[nd][2 * i] * mult, o[nd][2 * i + 1] * mult);
     }
+  }
   }
 }
 
@@ -390,8 +504,8 @@ head_linear_mma_kernel(const __nv_bfloat16* __restrict__ x, int64_t x_stride, in
 }
 
 template <int RANK, int ROT>
-size_t latent_mma_smem() {
-  return (size_t)LM_BM * (RANK + ROT) * 2 + 2 * (size_t)LM_BN * (RANK + ROT) * 2 + (size_t)LM_BM * (LM_BN + 2) * 4 +
+size_t latent_mma_smem(int q_rows) {
+  return (size_t)q_rows * (RANK + ROT) * 2 + 2 * (size_t)LM_BN * (RANK + ROT) * 2 + (size_t)LM_BM * (LM_BN + 2) * 4 +
          (size_t)LM_BM * LM_BN * 2 + 3 * LM_BM * 4;
 }
 
@@ -404,16 +518,25 @@ int latent_mma_launch(const __nv_bfloat16* qa, int64_t qa_stride, const __nv_bfl
                       float scale, int splits, int tiles_per_split, int* status, cudaStream_t stream) {
   const int gp = heads <= LM_BM ? heads : 1;
   const int qt = LM_BM / gp;
-  const size_t smem = latent_mma_smem<RANK, ROT>();
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(latent_mma_kernel<RANK, ROT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
+  const int rows_most = (max_q_len < qt ? max_q_len : qt) * gp;
+  const int q_rows = rows_most >= LM_BM ? LM_BM : ((rows_most + 15) / 16) * 16;
+  const size_t smem = latent_mma_smem<RANK, ROT>(q_rows);
+  static bool attr_set = false;
+  if (!attr_set && latent_mma_smem<RANK, ROT>(LM_BM) > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(latent_mma_kernel<RANK, ROT, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)latent_mma_smem<RANK, ROT>(LM_BM));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(latent_mma_kernel<RANK, ROT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)latent_mma_smem<RANK, ROT>(16));
     if (e != cudaSuccess) return (int)e;
+    attr_set = true;
   }
   dim3 grid(((max_q_len + qt - 1) / qt) * splits, heads / gp, num_requests);
-  int code = gllm_launch(latent_mma_kernel<RANK, ROT>, grid, dim3(LM_THREADS), smem, stream, qa, qa_stride, qr,
+  auto kernel = q_rows == 16 ? latent_mma_kernel<RANK, ROT, true> : latent_mma_kernel<RANK, ROT, false>;
+  int code = gllm_launch(kernel, grid, dim3(LM_THREADS), smem, stream, qa, qa_stride, qr,
                          qr_stride, qr_head, gate, gate_stride, out, out_stride, part_o, part_ml, cache, block_table,
-                         bt_stride, cu_q, ctx_lens, slots, n_tokens, heads, gp, qt, block_size, num_pages,
+                         bt_stride, cu_q, ctx_lens, slots, n_tokens, heads, gp, qt, q_rows, block_size, num_pages,
                          scale * LOG2E, splits, tiles_per_split, status);
   if (code != 0 || splits <= 1) return code;
   return gllm_launch(latent_merge_kernel, dim3((unsigned)(n_tokens * heads)), dim3(256), 0, stream,

@@ -279,6 +279,50 @@ def sigmoid_attention(tokens=2048, batch=1, context=0, hq=32, hkv=8, dk=64, dv=6
                    dict(tokens=tokens, batch=batch, context=context, heads=hq, kv_heads=hkv, dk=dk, dv=dv), nbytes, flops)
 
 
+def latent_attention(tokens=2048, batch=1, context=0, heads=16, rank=512, rot=64, block_size=16, iters=5, peaks=None,
+                     mma=1, split_keys=0):
+    """``batch`` requests of ``tokens`` new tokens over ``context`` cached ones (tokens=1: a decode step) through
+    the latent attention kernel (with its merge when the keys are cut into ranges).  FLOPs: both products over the
+    visible keys; bytes: every request's cached vectors once, the queries and the result."""
+    from gllm_b200.ops import latent
+
+    latent.USE_TENSOR_CORES = bool(mma)
+    if split_keys:
+        latent.SPLIT_KEYS = split_keys          # the shortest range of keys a CTA takes
+    dk = rank + rot
+    pages_per_req = -(-(context + tokens) // block_size)
+    num_pages = batch * pages_per_req + 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    pool = torch.randn((num_pages, block_size * dk), generator=g, device="cuda").to(torch.bfloat16)
+    table = torch.randperm(num_pages - 1, generator=g, device="cuda").to(torch.int32).view(batch, pages_per_req).contiguous()
+    q_head = 128 + rot
+    rows = torch.randn(batch * tokens, heads * q_head + 8 * (-(-heads // 8)), device="cuda").to(torch.bfloat16)
+    qa = torch.randn(batch * tokens, heads * rank, device="cuda").to(torch.bfloat16)
+    b = _Batch(batch, tokens, context)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: latent.attention_latent(qa, rows, q_head, 128, heads * q_head, pool, table, b.positions, b.token_row,
+                                         heads, rank, rot, block_size, dk ** -0.5, batch=b)
+    us = _time(fn, iters, flush)
+    flops = 2.0 * (dk + rank) * heads * batch * (tokens * context + tokens * (tokens + 1) / 2)
+    nbytes = batch * (context + tokens) * dk * 2 + qa.numel() * 4 + batch * tokens * heads * rot * 2
+    return _result("latent_attention (mma.sync)" if mma else "latent_attention (CUDA cores)", us, peaks,
+                   dict(tokens=tokens, batch=batch, context=context, heads=heads, rank=rank, rot=rot), nbytes, flops)
+
+
+def head_linear(tokens=2048, heads=16, inner=128, outer=512, iters=5, peaks=None, mma=1):
+    """One product per head, ``[tokens, inner] x [outer, inner]^T`` for each of ``heads`` heads in one launch."""
+    from gllm_b200.ops import latent
+
+    latent.USE_TENSOR_CORES = bool(mma)
+    x = torch.randn(tokens, heads * inner, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(heads, outer, inner, device="cuda") * 0.05).to(torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: latent.head_linear(x, inner, w), iters, flush)
+    return _result("head_linear (mma.sync)" if mma else "head_linear (CUDA cores)", us, peaks,
+                   dict(tokens=tokens, heads=heads, inner=inner, outer=outer),
+                   (x.numel() + w.numel() + tokens * heads * outer) * 2, 2.0 * tokens * heads * inner * outer)
+
+
 def matrix_recurrence(tokens=2048, batch=1, heads=16, dk=64, dv=128, mode=0, iters=5, peaks=None):
     """mode 0: gated linear attention; mode 1: the matrix memory with exponential gates."""
     from gllm_b200.ops import stateful
@@ -363,6 +407,8 @@ KERNELS = {
     "add_rmsnorm": add_rmsnorm,
     "argmax": argmax,
     "sigmoid_attention": sigmoid_attention,
+    "latent_attention": latent_attention,
+    "head_linear": head_linear,
     "matrix_recurrence": matrix_recurrence,
     "selective_scan": selective_scan,
     "conv_silu": conv_silu,

@@ -398,8 +398,9 @@ def test_one_product_per_head(dtype, n, heads, i, j, stride):
     torch.testing.assert_close(got.double(), want, rtol=tol, atol=tol)
 
 
+@pytest.mark.parametrize("single", [False, True])
 @pytest.mark.parametrize("heads,rank,rot", [(5, 64, 32), (16, 128, 64), (70, 96, 32), (3, 512, 64)])
-def test_latent_attention_on_the_tensor_cores_against_the_cuda_cores(heads, rank, rot):
+def test_latent_attention_on_the_tensor_cores_against_the_cuda_cores(heads, rank, rot, single):
     """Both kernels over the same pages: prompt portions beside single tokens over long contexts (whose keys are cut
     into ranges), with a gate; and both against a plain fp64 softmax."""
     from types import SimpleNamespace
@@ -409,7 +410,7 @@ def test_latent_attention_on_the_tensor_cores_against_the_cuda_cores(heads, rank
 
     g = torch.Generator().manual_seed(heads)
     block, dk = 16, rank + rot
-    q_lens, ctx_lens = [37, 1, 1, 5], [70, 900, 0, 333]
+    q_lens, ctx_lens = ([1, 1, 1], [900, 0, 333]) if single else ([37, 1, 1, 5], [70, 900, 0, 333])
     n, nreq = sum(q_lens), len(q_lens)
     pages_per = [-(-(c + q) // block) for c, q in zip(ctx_lens, q_lens)]
     num_pages = sum(pages_per) + 1
