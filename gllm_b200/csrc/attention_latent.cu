@@ -23,13 +23,15 @@
 namespace {
 
 // ------------------------------------------------------------------ latent_prep
+// The projection may arrive as `n_parts` unsummed fp32 splits of the product: they are summed into `rows` first.
 // row: [n, stride] of T; the query heads start at column 0, each `q_head` wide with its rotated part at
 // column `q_plain` of the head; the down-projection (rank + rot columns) starts at column `down_col`.
 // Rotation: neighbours (2i, 2i+1) of the first `rot_dims` columns of a rotated part, angle p * inv_freq[i].
 // Cache layer: [page][block_size][rank + rot].
 template <typename T>
 __global__ void __launch_bounds__(256)
-latent_prep_kernel(T* __restrict__ rows, int64_t stride, const float* __restrict__ norm_w, float eps,
+latent_prep_kernel(T* __restrict__ rows, int64_t stride, const float* __restrict__ parts, int n_parts,
+                   int64_t part_stride, int width, const float* __restrict__ norm_w, float eps,
                    const int* __restrict__ positions, const float* __restrict__ inv_freq,
                    const int* __restrict__ slot_mapping, T* __restrict__ cache, int n_tokens, int heads, int q_head,
                    int q_plain, int down_col, int rank, int rot, int rot_dims, int block_size, int num_pages,
@@ -40,6 +42,12 @@ latent_prep_kernel(T* __restrict__ rows, int64_t stride, const float* __restrict
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
   T* row = rows + (size_t)n * stride;
+  if (parts) {     // the projection arrives as unsummed splits [part][token][width]: summed in ascending order first
+    const float* src = parts + (size_t)n * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+      row[c] = from_float<T>(sum_parts16(src + c, n_parts, part_stride));
+    __syncthreads();
+  }
   const float pos = (float)positions[n];
   const int half = rot_dims / 2;
   // the rotated part of every query head, in place
@@ -223,14 +231,17 @@ attention_latent_kernel(const T* __restrict__ qa, int64_t qa_stride, int qa_head
 }
 
 template <typename T>
-int latent_prep_launch(T* rows, int64_t stride, const float* norm_w, float eps, const int* positions,
+int latent_prep_launch(T* rows, int64_t stride, const float* parts, int n_parts, int64_t part_stride, int width,
+                       const float* norm_w, float eps, const int* positions,
                        const float* inv_freq, const int* slot_mapping, T* cache, int n_tokens, int heads, int q_head,
                        int q_plain, int down_col, int rank, int rot, int rot_dims, int block_size, int num_pages,
                        int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2 || q_plain + rot > q_head)
+  if (rank <= 0 || rot < 0 || rot_dims < 0 || rot_dims > rot || rot_dims % 2 || q_plain + rot > q_head ||
+      n_parts > 16 || (parts && width > stride))
     return (int)cudaErrorInvalidValue;
-  return gllm_launch(latent_prep_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, stream, rows, stride, norm_w, eps,
+  return gllm_launch(latent_prep_kernel<T>, dim3((unsigned)n_tokens), dim3(256), 0, stream, rows, stride, parts,
+                     n_parts, part_stride, width, norm_w, eps,
                      positions, inv_freq, slot_mapping, cache, n_tokens, heads, q_head, q_plain, down_col, rank, rot,
                      rot_dims, block_size, num_pages, status);
 }
@@ -270,12 +281,14 @@ int attention_latent_launch(const T* qa, int64_t qa_stride, int qa_head, const T
 }  // namespace
 
 #define GLLM_LATENT_EXPORTS(T, S)                                                                                \
-  GLLM_API int gllm_latent_prep_##S(T* rows, int64_t stride, const float* norm_w, float eps, const int* positions, \
+  GLLM_API int gllm_latent_prep_##S(T* rows, int64_t stride, const float* parts, int n_parts, int64_t part_stride, \
+                                    int width, const float* norm_w, float eps, const int* positions,             \
                                     const float* inv_freq, const int* slot_mapping, T* cache, int n_tokens,      \
                                     int heads, int q_head, int q_plain, int down_col, int rank, int rot,         \
                                     int rot_dims, int block_size, int num_pages, int* status,                    \
                                     cudaStream_t stream) {                                                       \
-    return latent_prep_launch<T>(rows, stride, norm_w, eps, positions, inv_freq, slot_mapping, cache, n_tokens,  \
+    return latent_prep_launch<T>(rows, stride, parts, n_parts, part_stride, width, norm_w, eps, positions,       \
+                                 inv_freq, slot_mapping, cache, n_tokens,                                        \
                                  heads, q_head, q_plain, down_col, rank, rot, rot_dims, block_size, num_pages,   \
                                  status, stream);                                                                \
   }                                                                                                              \

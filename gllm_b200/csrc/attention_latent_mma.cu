@@ -374,7 +374,7 @@ latent_mma_kernel(const __nv_bfloat16* __restrict__ qa, int64_t qa_stride, const
 
 // Combines the ranges of latent_mma_kernel: out = sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s, times the gate.
 // One block per (token, head).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                     const __nv_bfloat16* __restrict__ gate, int64_t gate_stride, __nv_bfloat16* __restrict__ out,
                     int64_t out_stride, int n_tokens, int heads, int rank, int splits) {
@@ -405,12 +405,12 @@ latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   __syncthreads();
   for (int c = threadIdx.x; c < rank; c += blockDim.x) {
     float acc = 0.f;
-    for (int s0 = 0; s0 < splits; s0 += 8) {           // eight loads in flight, then eight additions in ascending order
-      float v[8];
+    for (int s0 = 0; s0 < splits; s0 += 16) {          // sixteen loads in flight, then the additions in ascending order
+      float v[16];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[k] = s0 + k < splits ? __ldcg(part_o + (base + (s0 + k) * step) * rank + c) : 0.f;
+      for (int k = 0; k < 16; ++k) v[k] = s0 + k < splits ? __ldcg(part_o + (base + (s0 + k) * step) * rank + c) : 0.f;
 #pragma unroll
-      for (int k = 0; k < 8; ++k) acc = fmaf(w_s[(s0 + k) & 63], v[k], acc);
+      for (int k = 0; k < 16; ++k) acc = fmaf(w_s[(s0 + k) & 63], v[k], acc);
     }
     out[token * out_stride + (int64_t)head * rank + c] = __float2bfloat16_rn(acc);
   }
@@ -539,7 +539,7 @@ int latent_mma_launch(const __nv_bfloat16* qa, int64_t qa_stride, const __nv_bfl
                          bt_stride, cu_q, ctx_lens, slots, n_tokens, heads, gp, qt, q_rows, block_size, num_pages,
                          scale * LOG2E, splits, tiles_per_split, status);
   if (code != 0 || splits <= 1) return code;
-  return gllm_launch(latent_merge_kernel, dim3((unsigned)(n_tokens * heads)), dim3(256), 0, stream,
+  return gllm_launch(latent_merge_kernel, dim3((unsigned)(n_tokens * heads)), dim3(RANK >= 512 ? 512 : 256), 0, stream,
                      (const float*)part_o, (const float*)part_ml, gate, gate_stride, out, out_stride, n_tokens, heads,
                      RANK, splits);
 }

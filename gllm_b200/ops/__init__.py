@@ -96,8 +96,8 @@ _SIGNATURES = {
                                        c_int, c_int, c_float, P, P],
     },
     "attention_latent": {
-        "gllm_latent_prep_{t}": [P, c_int64, P, c_float, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_int, c_int, P, P],
+        "gllm_latent_prep_{t}": [P, c_int64, P, c_int, c_int64, c_int, P, c_float, P, P, P, P, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, P, P],
         "gllm_head_linear_{t}": [P, c_int64, c_int, P, P, c_int64, c_int, c_int, c_int, c_int, c_int, P],
         "gllm_attention_latent_{t}": [P, c_int64, c_int, P, c_int64, c_int, P, c_int64, P, c_int64, c_int, P, P, c_int,
                                       P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P],

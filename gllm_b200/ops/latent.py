@@ -86,13 +86,24 @@ def _rows(t: torch.Tensor, name: str, dtype=None) -> None:
         raise ValueError(f"{name} must be [tokens, columns] with contiguous columns")
 
 
-def latent_prep(rows: torch.Tensor, norm_weight: torch.Tensor, eps: float, positions: torch.Tensor,
+def latent_prep(rows, norm_weight: torch.Tensor, eps: float, positions: torch.Tensor,
                 inv_freq: torch.Tensor, slot_mapping: torch.Tensor | None, pages: torch.Tensor, heads: int,
-                q_plain: int, rot: int, rank: int, down_col: int, block_size: int) -> None:
-    """On the projection rows ``[n, >= heads * (q_plain + rot) + rank + rot]``: rotate the last ``rot`` columns
-    of every query head in place (neighbouring pairs, ``2 * len(inv_freq)`` columns of them), and store
+                q_plain: int, rot: int, rank: int, down_col: int, block_size: int) -> torch.Tensor:
+    """On the projection rows ``[n, >= heads * (q_plain + rot) + rank + rot]`` (a tensor, or a SplitSum that is
+    summed into a new tensor first, in the same kernel): rotate the last ``rot`` columns of every query head in
+    place (neighbouring pairs, ``2 * len(inv_freq)`` columns of them), and store
     ``[rms(down[:rank]) * norm_weight ; rotate(down[rank:])]`` of the down-projection at column ``down_col``
-    into the token's cache slot.  ``pages`` is the pool layer ``[pages, block_size * (rank + rot)]``."""
+    into the token's cache slot.  ``pages`` is the pool layer ``[pages, block_size * (rank + rot)]``.  Returns the
+    rows."""
+    from gllm_b200.ops import SplitSum, _parts_args
+
+    parts_ptr, n_parts, part_stride = _parts_args(rows)
+    if isinstance(rows, SplitSum):
+        if n_parts > 16:
+            rows = rows.tensor()
+            parts_ptr, n_parts, part_stride = None, 0, 0
+        else:
+            rows = torch.empty(tuple(rows.shape), dtype=rows.dtype, device=rows.device)
     _rows(rows, "rows")
     _cuda(norm_weight, "norm_weight", torch.float32)
     _cuda(inv_freq, "inv_freq", torch.float32)
@@ -107,10 +118,11 @@ def latent_prep(rows: torch.Tensor, norm_weight: torch.Tensor, eps: float, posit
     if slot_mapping is not None:
         _cuda(slot_mapping, "slot_mapping", torch.int32)
     f = _fn("attention_latent", f"gllm_latent_prep_{_suffix(rows.dtype)}")
-    _check(f(rows.data_ptr(), rows.stride(0), norm_weight.data_ptr(), float(eps), positions.data_ptr(),
-             inv_freq.data_ptr(), _ptr(slot_mapping), pages.data_ptr(), rows.shape[0], int(heads),
-             int(q_plain + rot), int(q_plain), int(down_col), int(rank), int(rot), 2 * inv_freq.numel(),
+    _check(f(rows.data_ptr(), rows.stride(0), parts_ptr, n_parts, part_stride, rows.shape[1], norm_weight.data_ptr(),
+             float(eps), positions.data_ptr(), inv_freq.data_ptr(), _ptr(slot_mapping), pages.data_ptr(), rows.shape[0],
+             int(heads), int(q_plain + rot), int(q_plain), int(down_col), int(rank), int(rot), 2 * inv_freq.numel(),
              int(block_size), pages.shape[0], status_word(rows.device).data_ptr(), _stream()), "latent_prep")
+    return rows
 
 
 def head_linear(x: torch.Tensor, x_head: int, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
