@@ -59,9 +59,15 @@ def _attention_latent_mma(qa, rows, q_head, q_plain, gate_col, pages, block_tabl
     splits, tiles_per_split = 1, 0
     # (with more than half as many tiles as SMs the ranges cost more than they win: 512 tokens over 1,536 cached ones
     # 255 us in three ranges against 217 us in one; 128 tokens: 73 against 174 us)
-    if 2 * tiles <= sms and batch.max_seq_len > 2 * SPLIT_KEYS:
+    # The ranges have to cover the longest sequence of every step this launch serves.  A captured prompt portion
+    # is replayed for other contexts (the step's own longest sequence is then only that of the captured step), so
+    # under capture the bound is what a block-table row can hold; single tokens are captured per sequence bucket.
+    longest = batch.max_seq_len
+    if batch.max_q_len > 1 and torch.cuda.is_current_stream_capturing():
+        longest = max(longest, block_table.shape[1] * block_size)
+    if 2 * tiles <= sms and longest > 2 * SPLIT_KEYS:
         want = min(MAX_SPLITS, -(-2 * sms // tiles))
-        key_tiles = -(-batch.max_seq_len // KEY_TILE)
+        key_tiles = -(-longest // KEY_TILE)
         tiles_per_split = max(SPLIT_KEYS // KEY_TILE, -(-key_tiles // want))
         splits = -(-key_tiles // tiles_per_split)
     part_o = part_ml = None

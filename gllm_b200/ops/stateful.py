@@ -294,10 +294,15 @@ def _sigmoid_attention_mma(qkv, cache_pages, block_table, head_bias, heads, kv_h
     tiles = -(-batch.max_q_len // qt) * head_tiles * batch.num_requests
     sms = torch.cuda.get_device_properties(qkv.device).multi_processor_count
     splits, tiles_per_split = 1, 0
-    if tiles < 4 * sms and batch.max_seq_len > 2 * SPLIT_KEYS:
+    # a captured prompt portion is replayed for other contexts: under capture the ranges cover what a block-table
+    # row can hold, not just the captured step's longest sequence (single tokens are captured per sequence bucket)
+    longest = batch.max_seq_len
+    if batch.max_q_len > 1 and torch.cuda.is_current_stream_capturing():
+        longest = max(longest, block_table.shape[1] * block_size)
+    if tiles < 4 * sms and longest > 2 * SPLIT_KEYS:
         want = min(MAX_SPLITS, -(-8 * sms // tiles))          # five CTAs fit an SM: keep them all streaming
-        tiles_per_split = max(SPLIT_KEYS // 64, -(-(-(-batch.max_seq_len // 64)) // want))
-        splits = -(-(-(-batch.max_seq_len // 64)) // tiles_per_split)
+        tiles_per_split = max(SPLIT_KEYS // 64, -(-(-(-longest // 64)) // want))
+        splits = -(-(-(-longest // 64)) // tiles_per_split)
     partial = None
     if splits > 1:
         partial = batch.workspace.get("sigmoid_attention_partial", splits * n * heads * dv, torch.float32)

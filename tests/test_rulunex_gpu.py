@@ -265,6 +265,22 @@ def test_single_tokens_over_a_long_context(tmp_path):
     compare(run_steps(runner, steps), index, plain, BF16_TOL_MAX, BF16_TOL_MEAN)
 
 
+def test_a_captured_portion_replayed_over_a_longer_context(tmp_path):
+    """Portions of one size run as a CUDA graph captured on the first of them; the later ones replay it over a
+    context the captured step did not have.  With keys cut into ranges (few tiles, tensor-core latent kernel) the
+    ranges must cover those contexts too."""
+    from gllm_b200.engine.step import StepRunner
+
+    cfg = single_mixer("latent_wide")
+    weights, _, runner = make(cfg, tmp_path, "bfloat16", max_tokens=1024)
+    graphed = StepRunner(runner.model, runner.cache, max_tokens_per_step=1024, prefill_graph_tokens=(320,))
+    toks = torch.randint(0, cfg["vocab"], (960,), generator=torch.Generator().manual_seed(17)).tolist()
+    plain = {"r": plain_forward(cfg, weights, toks)}
+    steps, index = steps_of(toks, [320, 320, 320])
+    compare(run_steps(graphed, steps), index, plain, *tolerance("bfloat16"))
+    assert graphed.graph_replays == 2
+
+
 def test_a_slot_and_its_pages_used_again_start_clean(tmp_path):
     """One state slot and a pool of four pages: the second request gets the first one's slot and pages."""
     cfg = RULUNEX["A"]
