@@ -268,16 +268,25 @@ def test_single_tokens_over_a_long_context(tmp_path):
 def test_a_captured_portion_replayed_over_a_longer_context(tmp_path):
     """Portions of one size run as a CUDA graph captured on the first of them; the later ones replay it over a
     context the captured step did not have.  With keys cut into ranges (few tiles, tensor-core latent kernel) the
-    ranges must cover those contexts too."""
+    ranges must cover those contexts too: the one decisive key lies beyond the captured step's longest sequence."""
+    from gllm_b200.engine.replay import build_runner
     from gllm_b200.engine.step import StepRunner
 
-    cfg = single_mixer("latent_wide")
-    weights, _, runner = make(cfg, tmp_path, "bfloat16", max_tokens=1024)
+    cfg, weights = decisive_latent_model("latent_wide")
+    folder = write_model(cfg, weights, str(tmp_path / "model"))
+    _, runner = build_runner(folder, "bfloat16", 1024, block_size=16)
     graphed = StepRunner(runner.model, runner.cache, max_tokens_per_step=1024, prefill_graph_tokens=(320,))
-    toks = torch.randint(0, cfg["vocab"], (960,), generator=torch.Generator().manual_seed(17)).tolist()
-    plain = {"r": plain_forward(cfg, weights, toks)}
+    toks = torch.randint(3, cfg["vocab"], (960,), generator=torch.Generator().manual_seed(17)).tolist()
+    toks[500], toks[-1] = 1, 2
+    plain = plain_forward(cfg, weights, toks)
+    without = list(toks)
+    without[500] = 3
+    blind = plain_forward(cfg, weights, without)
+    tol_max, _ = tolerance("bfloat16")
+    scale = max(1.0, float(plain.abs().max()))
+    assert float((plain[-1] - blind[-1]).abs().max()) > 3 * tol_max * scale
     steps, index = steps_of(toks, [320, 320, 320])
-    compare(run_steps(graphed, steps), index, plain, *tolerance("bfloat16"))
+    compare(run_steps(graphed, steps), [i for i in index if i[3] >= 958], {"r": plain}, tol_max, None)
     assert graphed.graph_replays == 2
 
 
